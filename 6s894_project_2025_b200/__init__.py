@@ -1,0 +1,24 @@
+"""B200-native Walsh-Hadamard transform and fused W . H(X).
+
+The directory name starts with a digit, so import it with
+``importlib.import_module("6s894_project_2025_b200")``.
+"""
+from .ops import (  # noqa: F401
+    device_status,
+    fused_gemm_workspace_bytes,
+    fused_ht_gemm,
+    fused_ht_gemv,
+    hadamard_transform,
+)
+from .partition import gather_result, shard_tokens, token_range  # noqa: F401
+
+__all__ = [
+    "hadamard_transform",
+    "fused_ht_gemm",
+    "fused_ht_gemv",
+    "fused_gemm_workspace_bytes",
+    "device_status",
+    "token_range",
+    "shard_tokens",
+    "gather_result",
+]

@@ -1,0 +1,78 @@
+"""ctypes binding of libb200ht.so (the C ABI declared in include/b200ht.h).
+
+There is no CPU fallback: if the shared library is missing it is built with
+nvcc, and if that is impossible the import of an op raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from pathlib import Path
+
+_HERE = Path(__file__).resolve().parent
+LIB_PATH = _HERE / "libb200ht.so"
+
+F16, BF16, F32 = 0, 1, 2
+OUT_MN, OUT_NM = 0, 1
+
+# every symbol include/b200ht.h declares
+EXPORTS = (
+    "b200ht_version",
+    "b200ht_error_string",
+    "b200ht_fwht",
+    "b200ht_fused_gemm_workspace_bytes",
+    "b200ht_fused_gemm",
+    "b200ht_fused_gemv",
+    "b200ht_device_status",
+)
+
+_lock = threading.Lock()
+_lib = None
+
+
+def _declare(lib: ctypes.CDLL) -> None:
+    vp, i, f = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+    lib.b200ht_version.restype = i
+    lib.b200ht_version.argtypes = []
+    lib.b200ht_error_string.restype = ctypes.c_char_p
+    lib.b200ht_error_string.argtypes = [i]
+    lib.b200ht_fwht.restype = i
+    lib.b200ht_fwht.argtypes = [vp, vp, ctypes.c_uint64, ctypes.c_uint32, i, f, vp]
+    lib.b200ht_fused_gemm_workspace_bytes.restype = ctypes.c_size_t
+    lib.b200ht_fused_gemm_workspace_bytes.argtypes = [i, i, i, i]
+    lib.b200ht_fused_gemm.restype = i
+    lib.b200ht_fused_gemm.argtypes = [vp, vp, vp, i, i, i, i, i, i, f, vp, ctypes.c_size_t, vp]
+    lib.b200ht_fused_gemv.restype = i
+    lib.b200ht_fused_gemv.argtypes = [vp, vp, vp, i, i, i, i, i, f, vp]
+    lib.b200ht_device_status.restype = i
+    lib.b200ht_device_status.argtypes = [i]
+
+
+def load(build_if_missing: bool = True) -> ctypes.CDLL:
+    """Load (building first if needed) the shared library; raises if impossible."""
+    global _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if not LIB_PATH.exists():
+            if not build_if_missing:
+                raise RuntimeError(f"{LIB_PATH} is missing and there is no fallback implementation")
+            from .build import build
+
+            build()
+        lib = ctypes.CDLL(str(LIB_PATH))
+        for name in EXPORTS:
+            if not hasattr(lib, name):
+                raise RuntimeError(f"{LIB_PATH} does not export {name}")
+        _declare(lib)
+        _lib = lib
+        return lib
+
+
+def error_string(code: int) -> str:
+    return load().b200ht_error_string(int(code)).decode()
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        raise RuntimeError(f"{what} failed: {error_string(code)} (code {code})")

@@ -1,0 +1,72 @@
+// Version, error text, device check and the device status word.
+#include <mutex>
+
+#include "common.cuh"
+
+namespace b200ht {
+
+__device__ int g_status_word = 0;
+
+int *status_word_ptr()
+{
+    int *p = nullptr;
+    if (cudaGetSymbolAddress((void **)&p, g_status_word) != cudaSuccess) return nullptr;
+    return p;
+}
+
+int check_device()
+{
+    static std::mutex mu;
+    static int ok_mask[64] = {0};  // 0 unknown, 1 ok, 2 wrong architecture
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return B200HT_ERR_DEVICE;
+    std::lock_guard<std::mutex> lk(mu);
+    if (ok_mask[dev] == 0) {
+        int major = 0;
+        e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+        if (e != cudaSuccess) return (int)e;
+        ok_mask[dev] = (major == 10) ? 1 : 2;
+    }
+    return ok_mask[dev] == 1 ? 0 : B200HT_ERR_DEVICE;
+}
+
+}  // namespace b200ht
+
+extern "C" int b200ht_version(void) { return 100; }
+
+extern "C" const char *b200ht_error_string(int code)
+{
+    switch (code) {
+    case 0: return "success";
+    case B200HT_ERR_NULL: return "b200ht: a required pointer is NULL";
+    case B200HT_ERR_SIZE: return "b200ht: size must be a power of two in the supported range";
+    case B200HT_ERR_DTYPE: return "b200ht: unsupported element type";
+    case B200HT_ERR_ALIGN: return "b200ht: pointer is not 16-byte aligned";
+    case B200HT_ERR_WORKSPACE: return "b200ht: workspace missing or too small";
+    case B200HT_ERR_OVERLAP: return "b200ht: input and output partially overlap";
+    case B200HT_ERR_DEVICE: return "b200ht: current device is not an sm_100 (B200) GPU";
+    case B200HT_ERR_TIMEOUT: return "b200ht: a bounded device-side wait expired";
+    default: break;
+    }
+    if (code > 0) return cudaGetErrorString((cudaError_t)code);
+    return "b200ht: unknown error code";
+}
+
+extern "C" int b200ht_device_status(int clear)
+{
+    int rc = b200ht::check_device();
+    if (rc) return rc;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return (int)e;
+    int v = 0;
+    e = cudaMemcpyFromSymbol(&v, b200ht::g_status_word, sizeof(int));
+    if (e != cudaSuccess) return (int)e;
+    if (clear && v != 0) {
+        const int zero = 0;
+        e = cudaMemcpyToSymbol(b200ht::g_status_word, &zero, sizeof(int));
+        if (e != cudaSuccess) return (int)e;
+    }
+    return v;
+}

@@ -1,0 +1,179 @@
+// Fused C = W . H(X).  Replaces fused_ht_gemm_pipelined
+// (fused_ht/fusion_pipelined.cu:306-563).
+//
+// One call = transform of the token rows of X into a workspace that is sized to
+// stay L2-resident, followed on the same stream by the contraction against W.
+//   fp32 inputs: exact fp32 butterflies + FFMA GEMM (sgemm_nt_kernel, this file)
+//   bf16 inputs: 16-bit transform (fwht.cu) + tcgen05 GEMM (gemm_tcgen05.cu)
+#include "common.cuh"
+
+namespace b200ht {
+
+int launch_fwht(const void *in, void *out, uint64_t rows, uint32_t n, int dtype, float scale,
+                cudaStream_t st);
+int launch_gemm_bf16_tcgen05(const void *Y, const void *W, void *C, int M, int N, int K, int out_dtype,
+                             int out_layout, cudaStream_t st);
+
+// ---------------------------------------------------------------------------
+// C[m, n] = sum_k A[m, k] * Bm[n, k]   (both operands K-contiguous), fp32 FFMA.
+// 128 x 128 x 16 tiles, 256 threads, 8 x 8 outputs per thread, register-staged
+// double buffering.
+// ---------------------------------------------------------------------------
+constexpr int SG_BM = 128, SG_BN = 128, SG_BK = 16, SG_PAD = 4;
+
+__device__ __forceinline__ float4 sg_load4(const float *base, int row, int nrows, int k, int K, bool vec)
+{
+    float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (row < nrows) {
+        const float *p = base + (size_t)row * K + k;
+        if (vec && k + 3 < K) {
+            r = *(const float4 *)p;
+        } else {
+            if (k < K) r.x = p[0];
+            if (k + 1 < K) r.y = p[1];
+            if (k + 2 < K) r.z = p[2];
+            if (k + 3 < K) r.w = p[3];
+        }
+    }
+    return r;
+}
+
+template <int OUT_DT, int LAYOUT>
+__global__ void __launch_bounds__(256)
+sgemm_nt_kernel(const float *A, const float *Bm, void *C, int M, int N, int K, int vec)
+{
+    __shared__ __align__(16) float As[2][SG_BK][SG_BM + SG_PAD];
+    __shared__ __align__(16) float Bs[2][SG_BK][SG_BN + SG_PAD];
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int m0 = blockIdx.y * SG_BM, n0 = blockIdx.x * SG_BN;
+    float4 ra[2], rb[2];
+    const int lrow = tid >> 2, lk = (tid & 3) * 4;  // second half: row + 64
+
+    auto gload = [&](int kt) {
+        const int k = kt * SG_BK + lk;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            ra[i] = sg_load4(A, m0 + lrow + 64 * i, M, k, K, vec != 0);
+            rb[i] = sg_load4(Bm, n0 + lrow + 64 * i, N, k, K, vec != 0);
+        }
+    };
+    auto sstore = [&](int buf) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int r = lrow + 64 * i;
+            As[buf][lk + 0][r] = ra[i].x; As[buf][lk + 1][r] = ra[i].y;
+            As[buf][lk + 2][r] = ra[i].z; As[buf][lk + 3][r] = ra[i].w;
+            Bs[buf][lk + 0][r] = rb[i].x; Bs[buf][lk + 1][r] = rb[i].y;
+            Bs[buf][lk + 2][r] = rb[i].z; Bs[buf][lk + 3][r] = rb[i].w;
+        }
+    };
+
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+
+    const int ktiles = (K + SG_BK - 1) / SG_BK;
+    gload(0);
+    sstore(0);
+    __syncthreads();
+    for (int kt = 0; kt < ktiles; ++kt) {
+        const int buf = kt & 1;
+        if (kt + 1 < ktiles) gload(kt + 1);
+#pragma unroll
+        for (int k = 0; k < SG_BK; ++k) {
+            const float4 a0 = *(const float4 *)&As[buf][k][ty * 4];
+            const float4 a1 = *(const float4 *)&As[buf][k][64 + ty * 4];
+            const float4 b0 = *(const float4 *)&Bs[buf][k][tx * 4];
+            const float4 b1 = *(const float4 *)&Bs[buf][k][64 + tx * 4];
+            const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        if (kt + 1 < ktiles) sstore(buf ^ 1);
+        __syncthreads();
+    }
+
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int m = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
+        if (m >= M) continue;
+#pragma unroll
+        for (int jh = 0; jh < 2; ++jh) {
+            const int n = n0 + jh * 64 + tx * 4;
+            if (LAYOUT == B200HT_OUT_MN && OUT_DT == B200HT_F32 && (N & 3) == 0 && n + 3 < N) {
+                *(float4 *)((float *)C + (size_t)m * N + n) =
+                    make_float4(acc[i][jh * 4], acc[i][jh * 4 + 1], acc[i][jh * 4 + 2], acc[i][jh * 4 + 3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (n + j < N) {
+                        const size_t idx = LAYOUT == B200HT_OUT_MN ? (size_t)m * N + n + j : (size_t)(n + j) * M + m;
+                        if (OUT_DT == B200HT_F32) ((float *)C)[idx] = acc[i][jh * 4 + j];
+                        else ((__nv_bfloat16 *)C)[idx] = __float2bfloat16_rn(acc[i][jh * 4 + j]);
+                    }
+                }
+            }
+        }
+    }
+}
+
+static int launch_sgemm(const float *A, const float *Bm, void *C, int M, int N, int K, int out_dtype,
+                        int out_layout, cudaStream_t st)
+{
+    dim3 grid((N + SG_BN - 1) / SG_BN, (M + SG_BM - 1) / SG_BM);
+    const int vec = ((K & 3) == 0 && aligned16(A) && aligned16(Bm)) ? 1 : 0;
+    if (out_dtype == B200HT_F32) {
+        if (out_layout == B200HT_OUT_MN)
+            sgemm_nt_kernel<B200HT_F32, B200HT_OUT_MN><<<grid, 256, 0, st>>>(A, Bm, C, M, N, K, vec);
+        else
+            sgemm_nt_kernel<B200HT_F32, B200HT_OUT_NM><<<grid, 256, 0, st>>>(A, Bm, C, M, N, K, vec);
+    } else {
+        if (out_layout == B200HT_OUT_MN)
+            sgemm_nt_kernel<B200HT_BF16, B200HT_OUT_MN><<<grid, 256, 0, st>>>(A, Bm, C, M, N, K, vec);
+        else
+            sgemm_nt_kernel<B200HT_BF16, B200HT_OUT_NM><<<grid, 256, 0, st>>>(A, Bm, C, M, N, K, vec);
+    }
+    return (int)cudaGetLastError();
+}
+
+}  // namespace b200ht
+
+extern "C" size_t b200ht_fused_gemm_workspace_bytes(int M, int N, int K, int in_dtype)
+{
+    (void)M;
+    if (N <= 0 || K <= 0) return 0;
+    const size_t esz = in_dtype == B200HT_F32 ? 4 : 2;
+    size_t bytes = (size_t)N * (size_t)K * esz;
+    return (bytes + 255) & ~(size_t)255;
+}
+
+extern "C" int b200ht_fused_gemm(const void *X, const void *W, void *C, int M, int N, int K, int in_dtype,
+                                 int out_dtype, int out_layout, float scale, void *workspace,
+                                 size_t workspace_bytes, void *stream)
+{
+    using namespace b200ht;
+    if (in_dtype != B200HT_F32 && in_dtype != B200HT_BF16) return B200HT_ERR_DTYPE;
+    if (out_dtype != B200HT_F32 && out_dtype != B200HT_BF16) return B200HT_ERR_DTYPE;
+    if (out_layout != B200HT_OUT_MN && out_layout != B200HT_OUT_NM) return B200HT_ERR_SIZE;
+    if (K < 2 || K > (1 << kMaxLogN) || !is_pow2((uint64_t)K)) return B200HT_ERR_SIZE;
+    if (M < 0 || N < 0) return B200HT_ERR_SIZE;
+    if (M == 0 || N == 0) return 0;
+    if (!X || !W || !C) return B200HT_ERR_NULL;
+    if (!aligned16(X) || !aligned16(W) || !aligned16(C)) return B200HT_ERR_ALIGN;
+    const size_t need = b200ht_fused_gemm_workspace_bytes(M, N, K, in_dtype);
+    if (!workspace || workspace_bytes < need) return B200HT_ERR_WORKSPACE;
+    if (((uintptr_t)workspace & 255u) != 0) return B200HT_ERR_ALIGN;
+    int rc = check_device();
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    rc = launch_fwht(X, workspace, (uint64_t)N, (uint32_t)K, in_dtype, scale, st);
+    if (rc) return rc;
+    if (in_dtype == B200HT_F32)
+        return launch_sgemm((const float *)W, (const float *)workspace, C, M, N, K, out_dtype, out_layout, st);
+    return launch_gemm_bf16_tcgen05(workspace, W, C, M, N, K, out_dtype, out_layout, st);
+}

@@ -1,0 +1,346 @@
+// Standalone Walsh-Hadamard transform along the last dimension of a row-major
+// (rows x n) array.  Replaces the reference's hadamard_transform_ker and its
+// RowHandler strategies (csrc/main.cu:12-40, csrc/hada_handler.cuh:78-219).
+//
+// HBM-bound: 2 B read + 2 B written per element, ~15 butterfly stages of
+// arithmetic per element at n = 2^15.  The 16x16 Hadamard blocks run on the
+// tensor cores (mma.sync m16n8k16, fp32 accumulate) so the arithmetic stays far
+// below the memory time; data moves with 16-byte, fully coalesced accesses.
+//
+//   n = 8 .. 2048   fwht_reg_kernel : a warp keeps whole rows in registers
+//   n = 4096 .. 32768 fwht_smem_kernel: a CTA keeps a slab of rows in padded
+//                     shared memory; low 8 index bits in pass 1, the rest in pass 2
+//   n = 2, 4        fwht_tiny_kernel : one thread per row
+//   fp32            fwht_f32_kernel  : exact fp32 butterflies in shared memory
+#include "common.cuh"
+#include "fwht_f32.cuh"
+
+namespace b200ht {
+
+// ---------------------------------------------------------------------------
+// n <= 2048, 16-bit: rows live in one warp's registers.
+// A warp owns GRP consecutive 256-element chunks (GRP*32 16-byte vectors).
+// ---------------------------------------------------------------------------
+template <int DT, int LOGN>
+__global__ void __launch_bounds__(256) fwht_reg_kernel(const uint4 *in, uint4 *out,
+                                                       uint64_t total_vec, float mult)
+{
+    constexpr int P = LOGN < 8 ? LOGN : 8;
+    constexpr int CPR = LOGN > 8 ? (1 << (LOGN - 8)) : 1;  // chunks per row
+    constexpr int GRP = CPR > 4 ? CPR : 4;
+    const int lane = threadIdx.x & 31;
+    const uint64_t warp = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const uint64_t first = warp * (uint64_t)(GRP * 32);
+    if (first >= total_vec) return;
+
+    constexpr unsigned M1 = rot8_mask1(P), M2 = rot8_mask2(P);
+    uint32_t A1[4], A2[4];
+    make_hfrag<DT>(A1, lane, M1, hfrag_c(popc4(M1)));
+    make_hfrag<DT>(A2, lane, M2, hfrag_c(popc4(M2)));
+
+    uint4 v[GRP];
+#pragma unroll
+    for (int g = 0; g < GRP; ++g) {
+        const uint64_t idx = first + (uint64_t)g * 32 + lane;
+        v[g] = idx < total_vec ? ld_stream(in + idx) : make_uint4(0, 0, 0, 0);
+    }
+    float o[GRP][8];
+#pragma unroll
+    for (int g = 0; g < GRP; ++g) {
+        const uint32_t w[4] = {v[g].x, v[g].y, v[g].z, v[g].w};
+        rot8<DT>(w, o[g], A1, A2);
+    }
+    // index bits 8.. : butterflies across the chunks of a row, fp32
+#pragma unroll
+    for (int s = 1; s < CPR; s <<= 1) {
+#pragma unroll
+        for (int g = 0; g < GRP; ++g) {
+            if (!(g & s)) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float x = o[g][e], y = o[g | s][e];
+                    o[g][e] = x + y;
+                    o[g | s][e] = x - y;
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int g = 0; g < GRP; ++g) {
+        const uint64_t idx = first + (uint64_t)g * 32 + lane;
+        if (idx < total_vec) {
+            uint4 r;
+            r.x = pack2<DT>(o[g][0] * mult, o[g][1] * mult);
+            r.y = pack2<DT>(o[g][2] * mult, o[g][3] * mult);
+            r.z = pack2<DT>(o[g][4] * mult, o[g][5] * mult);
+            r.w = pack2<DT>(o[g][6] * mult, o[g][7] * mult);
+            st_stream(out + idx, r);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// n = 4096 .. 32768, 16-bit: a CTA of 8 warps holds a slab of SLAB_ROWS rows in
+// shared memory.  Chunk c (256 elements = 32 vectors) sits at vector offset 33*c
+// so that both the contiguous accesses of pass 1 and the chunk-strided accesses
+// of pass 2 are bank-conflict free.
+//   pass 1: every chunk: index bits 0..7, result rounded to 16 bit into smem
+//   pass 2: index bits 8..LOGN-1: five of them on the lanes through rot8 with
+//           identity on the in-lane bits, the rest as fp32 register butterflies
+//   pass 3: coalesced copy-out
+// ---------------------------------------------------------------------------
+template <int LOGN>
+struct SmemCfg {
+    static constexpr int Q = LOGN - 8;
+    static constexpr int SLAB_ROWS = LOGN >= 13 ? 1 : (1 << (13 - LOGN));
+    static constexpr int CPR = 1 << Q;
+    static constexpr int NCHUNK = SLAB_ROWS * CPR;
+    static constexpr int SMEM_BYTES = NCHUNK * 33 * 16;
+};
+
+template <int DT, int LOGN>
+__global__ void __launch_bounds__(256) fwht_smem_kernel(const uint4 *in, uint4 *out, uint64_t rows,
+                                                        float mult)
+{
+    using Cfg = SmemCfg<LOGN>;
+    constexpr int Q = Cfg::Q, CPR = Cfg::CPR;
+    extern __shared__ uint4 sm[];
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const uint64_t row0 = (uint64_t)blockIdx.x * Cfg::SLAB_ROWS;
+    const int rows_here = (int)((rows - row0) < (uint64_t)Cfg::SLAB_ROWS ? (rows - row0)
+                                                                          : (uint64_t)Cfg::SLAB_ROWS);
+    const int chunks_here = rows_here * CPR;
+    const uint4 *gin = in + row0 * (uint64_t)(CPR * 32);
+    uint4 *gout = out + row0 * (uint64_t)(CPR * 32);
+
+    uint32_t A1[4], A2[4];
+    make_hfrag<DT>(A1, lane, 15u, 0.25f);
+    make_hfrag<DT>(A2, lane, 15u, 0.25f);
+
+    constexpr int U = 4;
+    for (int c0 = warp; c0 < chunks_here; c0 += 8 * U) {
+        uint4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int c = c0 + 8 * u;
+            if (c < chunks_here) v[u] = ld_stream(gin + c * 32 + lane);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int c = c0 + 8 * u;
+            if (c < chunks_here) {
+                const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+                float o[8];
+                rot8<DT>(w, o, A1, A2);
+                uint4 r;
+                r.x = pack2<DT>(o[0], o[1]);
+                r.y = pack2<DT>(o[2], o[3]);
+                r.z = pack2<DT>(o[4], o[5]);
+                r.w = pack2<DT>(o[6], o[7]);
+                sm[c * 33 + lane] = r;
+            }
+        }
+    }
+    __syncthreads();
+
+    // pass 2: lanes <-> chunk-index bits 0..4 of the row (element bits 8..12)
+    constexpr unsigned M2 = Q >= 5 ? 7u : 3u;
+    make_hfrag<DT>(A1, lane, 6u, 0.5f);
+    make_hfrag<DT>(A2, lane, M2, 0.5f);
+    constexpr int J = Q > 5 ? (1 << (Q - 5)) : 1;
+    const int nitems = Q >= 5 ? rows_here * 32 : rows_here * 16;
+    for (int item = warp; item < nitems; item += 8) {
+        int slot, chunk0;
+        if constexpr (Q >= 5) {
+            slot = item & 31;
+            chunk0 = (item >> 5) * CPR + lane;
+        } else {
+            slot = 2 * (item & 15) + (lane >> 4);
+            chunk0 = (item >> 4) * CPR + (lane & 15);
+        }
+        float o[J][8];
+#pragma unroll
+        for (int j = 0; j < J; ++j) {
+            const uint4 t = sm[(chunk0 + 32 * j) * 33 + slot];
+            const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+            rot8<DT>(w, o[j], A1, A2);
+        }
+#pragma unroll
+        for (int s = 1; s < J; s <<= 1) {
+#pragma unroll
+            for (int j = 0; j < J; ++j) {
+                if (!(j & s)) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const float x = o[j][e], y = o[j | s][e];
+                        o[j][e] = x + y;
+                        o[j | s][e] = x - y;
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < J; ++j) {
+            uint4 r;
+            r.x = pack2<DT>(o[j][0] * mult, o[j][1] * mult);
+            r.y = pack2<DT>(o[j][2] * mult, o[j][3] * mult);
+            r.z = pack2<DT>(o[j][4] * mult, o[j][5] * mult);
+            r.w = pack2<DT>(o[j][6] * mult, o[j][7] * mult);
+            sm[(chunk0 + 32 * j) * 33 + slot] = r;
+        }
+    }
+    __syncthreads();
+
+    for (int c = warp; c < chunks_here; c += 8) st_stream(gout + c * 32 + lane, sm[c * 33 + lane]);
+}
+
+// ---------------------------------------------------------------------------
+// n = 2, 4 (16-bit): one thread per row.
+// ---------------------------------------------------------------------------
+template <int DT>
+__global__ void fwht_tiny_kernel(const uint16_t *in, uint16_t *out, uint64_t rows, int n, float scale)
+{
+    const uint64_t r = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= rows) return;
+    float v[4];
+    for (int i = 0; i < n; ++i) {
+        const uint32_t u = in[r * n + i];
+        v[i] = unpack2<DT>(u).x;
+    }
+    if (n == 2) {
+        const float a = v[0], b = v[1];
+        v[0] = a + b; v[1] = a - b;
+    } else {
+        const float a = v[0] + v[1], b = v[0] - v[1], c = v[2] + v[3], d = v[2] - v[3];
+        v[0] = a + c; v[1] = b + d; v[2] = a - c; v[3] = b - d;
+    }
+    for (int i = 0; i < n; ++i) out[r * n + i] = to_b16<DT>(v[i] * scale);
+}
+
+// ---------------------------------------------------------------------------
+// fp32: exact butterflies on a slab of max(n, 2048) floats in shared memory.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) fwht_f32_kernel(const float *in, float *out, uint64_t rows,
+                                                       int logn, int slab_rows, float scale)
+{
+    extern __shared__ float sf[];
+    const int n = 1 << logn;
+    const uint64_t row0 = (uint64_t)blockIdx.x * slab_rows;
+    const int rows_here = (int)((rows - row0) < (uint64_t)slab_rows ? (rows - row0) : (uint64_t)slab_rows);
+    const int total = rows_here * n;
+    const float *gin = in + row0 * n;
+    float *gout = out + row0 * n;
+    for (int i = threadIdx.x; i < total; i += blockDim.x) sf[i] = gin[i];
+    __syncthreads();
+    slab_fwht_f32(sf, total, logn, threadIdx.x, blockDim.x);
+    for (int i = threadIdx.x; i < total; i += blockDim.x) gout[i] = sf[i] * scale;
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+template <int DT, int LOGN>
+static int launch_reg(const void *in, void *out, uint64_t rows, float scale, cudaStream_t st)
+{
+    constexpr int P = LOGN < 8 ? LOGN : 8;
+    constexpr int CPR = LOGN > 8 ? (1 << (LOGN - 8)) : 1;
+    constexpr int GRP = CPR > 4 ? CPR : 4;
+    const uint64_t total_vec = (rows << LOGN) >> 3;
+    const uint64_t warps = (total_vec + GRP * 32 - 1) / (GRP * 32);
+    const uint64_t blocks = (warps + 7) / 8;
+    if (blocks > 0x7fffffffull) return B200HT_ERR_SIZE;
+    const float f = hfrag_c(popc4(rot8_mask1(P))) * hfrag_c(popc4(rot8_mask2(P)));
+    fwht_reg_kernel<DT, LOGN><<<(unsigned)blocks, 256, 0, st>>>((const uint4 *)in, (uint4 *)out,
+                                                                 total_vec, scale / f);
+    return (int)cudaGetLastError();
+}
+
+template <int DT, int LOGN>
+static int launch_smem(const void *in, void *out, uint64_t rows, float scale, cudaStream_t st)
+{
+    using Cfg = SmemCfg<LOGN>;
+    const uint64_t blocks = (rows + Cfg::SLAB_ROWS - 1) / Cfg::SLAB_ROWS;
+    if (blocks > 0x7fffffffull) return B200HT_ERR_SIZE;
+    cudaError_t e = cudaFuncSetAttribute(fwht_smem_kernel<DT, LOGN>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    fwht_smem_kernel<DT, LOGN><<<(unsigned)blocks, 256, Cfg::SMEM_BYTES, st>>>(
+        (const uint4 *)in, (uint4 *)out, rows, scale * 64.0f);
+    return (int)cudaGetLastError();
+}
+
+template <int DT>
+static int launch_b16(const void *in, void *out, uint64_t rows, int logn, float scale, cudaStream_t st)
+{
+    switch (logn) {
+    case 1:
+    case 2: {
+        const uint64_t blocks = (rows + 255) / 256;
+        if (blocks > 0x7fffffffull) return B200HT_ERR_SIZE;
+        fwht_tiny_kernel<DT><<<(unsigned)blocks, 256, 0, st>>>((const uint16_t *)in, (uint16_t *)out, rows,
+                                                              1 << logn, scale);
+        return (int)cudaGetLastError();
+    }
+    case 3: return launch_reg<DT, 3>(in, out, rows, scale, st);
+    case 4: return launch_reg<DT, 4>(in, out, rows, scale, st);
+    case 5: return launch_reg<DT, 5>(in, out, rows, scale, st);
+    case 6: return launch_reg<DT, 6>(in, out, rows, scale, st);
+    case 7: return launch_reg<DT, 7>(in, out, rows, scale, st);
+    case 8: return launch_reg<DT, 8>(in, out, rows, scale, st);
+    case 9: return launch_reg<DT, 9>(in, out, rows, scale, st);
+    case 10: return launch_reg<DT, 10>(in, out, rows, scale, st);
+    case 11: return launch_reg<DT, 11>(in, out, rows, scale, st);
+    case 12: return launch_smem<DT, 12>(in, out, rows, scale, st);
+    case 13: return launch_smem<DT, 13>(in, out, rows, scale, st);
+    case 14: return launch_smem<DT, 14>(in, out, rows, scale, st);
+    case 15: return launch_smem<DT, 15>(in, out, rows, scale, st);
+    }
+    return B200HT_ERR_SIZE;
+}
+
+int launch_fwht_f32(const float *in, float *out, uint64_t rows, int logn, float scale, cudaStream_t st)
+{
+    const int n = 1 << logn;
+    const int slab = n >= 2048 ? n : 2048;
+    const int slab_rows = slab / n;
+    const uint64_t blocks = (rows + slab_rows - 1) / slab_rows;
+    if (blocks > 0x7fffffffull) return B200HT_ERR_SIZE;
+    const int smem = slab * 4;
+    cudaError_t e = cudaFuncSetAttribute(fwht_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    fwht_f32_kernel<<<(unsigned)blocks, 256, smem, st>>>(in, out, rows, logn, slab_rows, scale);
+    return (int)cudaGetLastError();
+}
+
+int launch_fwht(const void *in, void *out, uint64_t rows, uint32_t n, int dtype, float scale,
+                cudaStream_t st)
+{
+    const int logn = ilog2(n);
+    if (dtype == B200HT_F32) return launch_fwht_f32((const float *)in, (float *)out, rows, logn, scale, st);
+    if (dtype == B200HT_BF16) return launch_b16<B200HT_BF16>(in, out, rows, logn, scale, st);
+    return launch_b16<B200HT_F16>(in, out, rows, logn, scale, st);
+}
+
+}  // namespace b200ht
+
+extern "C" int b200ht_fwht(const void *in, void *out, uint64_t rows, uint32_t n, int dtype, float scale,
+                           void *stream)
+{
+    using namespace b200ht;
+    if (dtype != B200HT_F16 && dtype != B200HT_BF16 && dtype != B200HT_F32) return B200HT_ERR_DTYPE;
+    if (!is_pow2(n) || n < 2 || n > (1u << kMaxLogN)) return B200HT_ERR_SIZE;
+    if (rows == 0) return 0;
+    if (!in || !out) return B200HT_ERR_NULL;
+    if (!aligned16(in) || !aligned16(out)) return B200HT_ERR_ALIGN;
+    const uint64_t esz = dtype == B200HT_F32 ? 4 : 2;
+    if (rows > (~0ull) / ((uint64_t)n * esz)) return B200HT_ERR_SIZE;
+    const uint64_t bytes = rows * n * esz;
+    if (in != out) {
+        const uintptr_t a = (uintptr_t)in, b = (uintptr_t)out;
+        if (a < b + bytes && b < a + bytes) return B200HT_ERR_OVERLAP;
+    }
+    int rc = check_device();
+    if (rc) return rc;
+    return launch_fwht(in, out, rows, n, dtype, scale, (cudaStream_t)stream);
+}

@@ -1,0 +1,320 @@
+// bf16 x bf16 -> fp32 contraction  C[m, t] = sum_k W[m, k] * Y[t, k]  on the
+// 5th-generation tensor cores.  Y = scale * H(X) is the transformed token
+// matrix produced by fwht.cu; this kernel is the second phase of
+// b200ht_fused_gemm for bf16 inputs and replaces the scalar-FMA GEMM of
+// fused_ht_gemm_pipelined (fused_ht/fusion_pipelined.cu:468-543).
+//
+// Persistent, warp-specialised, one CTA per SM:
+//   warp 0      TMA producer: W tile (128 x 64) and Y tile (256 x 64) per stage,
+//               128-byte swizzle, 4-stage mbarrier ring
+//   warp 1      allocates TMEM (512 columns = two 128 x 256 fp32 accumulators)
+//               and issues tcgen05.mma (M=128, N=256, K=16) from one thread
+//   warps 2..5  epilogue: tcgen05.ld of the finished accumulator, convert,
+//               store, while the next tile accumulates in the other TMEM half
+// Every mbarrier wait is time-limited; on expiry the CTA drains and exits and
+// the device status word carries B200HT_ERR_TIMEOUT.
+#include <mutex>
+
+#include "tc_common.cuh"
+
+namespace b200ht {
+
+constexpr int TC_BM = 128, TC_BN = 256, TC_BK = 64, TC_STAGES = 4;
+constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;  // 16 KB
+constexpr int TC_B_BYTES = TC_BN * TC_BK * 2;  // 32 KB
+constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
+constexpr int TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+
+template <int OUT_DT, int LAYOUT>
+__device__ __forceinline__ void tc_store_chunk(void *C, int M, int N, int m, int n, const uint32_t (&r)[32])
+{
+    if (m >= M || n >= N) return;
+    if constexpr (LAYOUT == B200HT_OUT_NM) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            if (n + j < N) {
+                const size_t idx = (size_t)(n + j) * M + m;
+                if constexpr (OUT_DT == B200HT_F32) ((float *)C)[idx] = __uint_as_float(r[j]);
+                else ((__nv_bfloat16 *)C)[idx] = __float2bfloat16_rn(__uint_as_float(r[j]));
+            }
+        }
+    } else {
+        if constexpr (OUT_DT == B200HT_F32) {
+            float *p = (float *)C + (size_t)m * N + n;
+            if ((N & 3) == 0 && n + 32 <= N) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                    *(float4 *)(p + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                     __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (n + j < N) p[j] = __uint_as_float(r[j]);
+            }
+        } else {
+            __nv_bfloat16 *p = (__nv_bfloat16 *)C + (size_t)m * N + n;
+            if ((N & 7) == 0 && n + 32 <= N) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                    uint4 v;
+                    v.x = pack2<B200HT_BF16>(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+                    v.y = pack2<B200HT_BF16>(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                    v.z = pack2<B200HT_BF16>(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+                    v.w = pack2<B200HT_BF16>(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+                    *(uint4 *)(p + j) = v;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (n + j < N) p[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+            }
+        }
+    }
+}
+
+// Tile order: groups of TC_GROUP_M row blocks of W; inside a group the token
+// blocks advance slowest, so the W rows of a group (and the few token blocks
+// in flight) stay L2-resident while the whole token range streams past them.
+constexpr int TC_GROUP_M = 16;
+__device__ __forceinline__ void tc_tile_coord(int tile, int mt, int nt, int &mb, int &nb)
+{
+    const int per_group = TC_GROUP_M * nt;
+    const int grp = tile / per_group;
+    const int rem = tile - grp * per_group;
+    const int gsz = (mt - grp * TC_GROUP_M) < TC_GROUP_M ? (mt - grp * TC_GROUP_M) : TC_GROUP_M;
+    nb = rem / gsz;
+    mb = grp * TC_GROUP_M + (rem - nb * gsz);
+}
+
+template <int OUT_DT, int LAYOUT>
+__global__ void __launch_bounds__(192, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmY, void *C, int M,
+               int N, int K, int *status)
+{
+    extern __shared__ unsigned char smem_dyn[];
+    const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+    const uint32_t bar_base = base + TC_STAGES * TC_STAGE_BYTES;
+    // barriers: full[S], empty[S], tmem_full[2], tmem_empty[2]; then tmem address slot, abort flag
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (TC_STAGES + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * TC_STAGES + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * TC_STAGES + 2 + a); };
+    unsigned char *gen_base = smem_dyn + (base - smem_u32(smem_dyn));
+    uint32_t *tmem_slot = (uint32_t *)(gen_base + TC_STAGES * TC_STAGE_BYTES + 8 * (2 * TC_STAGES + 4));
+    volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 4);  // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        tma_prefetch_desc(&tmW);
+        tma_prefetch_desc(&tmY);
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int mt = (M + TC_BM - 1) / TC_BM, nt = (N + TC_BN - 1) / TC_BN;
+    const int ntiles = mt * nt;
+    const int kblocks = K / TC_BK;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+                int mb, nb;
+                tc_tile_coord(tile, mt, nt, mb, nb);
+                const int m0 = mb * TC_BM, n0 = nb * TC_BN;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % TC_STAGES;
+                    const uint32_t ph = (it / TC_STAGES) & 1u;
+                    if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, status)) { ok = false; break; }
+                    mbar_expect_tx(full_bar(s), TC_STAGE_BYTES);
+                    const uint32_t sa = base + s * TC_STAGE_BYTES;
+                    tma_load_2d(sa, &tmW, kb * TC_BK, m0, full_bar(s));
+                    tma_load_2d(sa + TC_A_BYTES, &tmY, kb * TC_BK, n0, full_bar(s));
+                }
+            }
+            if (!ok) {
+                // copies already issued still land in this CTA's shared memory: give them time
+                const uint32_t pending = it < (uint32_t)TC_STAGES ? it : (uint32_t)TC_STAGES;
+                for (uint32_t j = 0; j < pending; ++j) {
+                    const uint32_t i2 = it - 1 - j;
+                    const uint64_t t0 = global_ns();
+                    while (!mbar_test(full_bar(i2 % TC_STAGES), (i2 / TC_STAGES) & 1u) &&
+                           global_ns() - t0 < 100000000ull) {}
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16(TC_BM, TC_BN);
+            uint32_t it = 0, tcount = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tcount) {
+                const int acc = tcount & 1;
+                const uint32_t aph = (tcount >> 1) & 1u;
+                if (!mbar_wait(tempty_bar(acc), aph ^ 1u, abort_flag, status)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * TC_BN;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % TC_STAGES;
+                    const uint32_t ph = (it / TC_STAGES) & 1u;
+                    if (!mbar_wait(full_bar(s), ph, abort_flag, status)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = base + s * TC_STAGE_BYTES;
+                    const uint64_t adesc = umma_desc_k_sw128(sa);
+                    const uint64_t bdesc = umma_desc_k_sw128(sa + TC_A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; ++k)
+                        umma_bf16_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) ? 1u : 0u);
+                    umma_commit(empty_bar(s));
+                }
+                if (ok) umma_commit(tfull_bar(acc));
+            }
+        }
+        __syncwarp();
+    } else {
+        const int q = warp & 3;  // TMEM lane quadrant this warp may read
+        uint32_t tcount = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tcount) {
+            const int acc = tcount & 1;
+            const uint32_t aph = (tcount >> 1) & 1u;
+            int mb, nb;
+            tc_tile_coord(tile, mt, nt, mb, nb);
+            const int m0 = mb * TC_BM, n0 = nb * TC_BN;
+            if (!mbar_wait(tfull_bar(acc), aph, abort_flag, status)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * TC_BN;
+            const int m = m0 + q * 32 + lane;
+#pragma unroll 1
+            for (int c = 0; c < TC_BN; c += 32) {
+                uint32_t r[32];
+                tmem_ld32(taddr + c, r);
+                tmem_ld_wait();
+                tc_store_chunk<OUT_DT, LAYOUT>(C, M, N, m, n0 + c, r);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(acc));
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// K < 64 (the 128-byte swizzled tile needs 64 bf16 per row): plain SIMT kernel.
+// ---------------------------------------------------------------------------
+__global__ void gemm_bf16_smallk_kernel(const __nv_bfloat16 *Y, const __nv_bfloat16 *W, void *C, int M, int N,
+                                        int K, int out_dtype, int out_layout)
+{
+    const int n = blockIdx.x * blockDim.x + threadIdx.x;
+    const int m = blockIdx.y * blockDim.y + threadIdx.y;
+    if (m >= M || n >= N) return;
+    float acc = 0.f;
+    for (int k = 0; k < K; ++k)
+        acc = fmaf(__bfloat162float(W[(size_t)m * K + k]), __bfloat162float(Y[(size_t)n * K + k]), acc);
+    const size_t idx = out_layout == B200HT_OUT_MN ? (size_t)m * N + n : (size_t)n * M + m;
+    if (out_dtype == B200HT_F32) ((float *)C)[idx] = acc;
+    else ((__nv_bfloat16 *)C)[idx] = __float2bfloat16_rn(acc);
+}
+
+// ---------------------------------------------------------------------------
+// host
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn()
+{
+    static std::mutex mu;
+    static EncodeTiledFn fn = nullptr;
+    std::lock_guard<std::mutex> lk(mu);
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+int encode_tmap_bf16_2d(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows)
+{
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return (int)cudaErrorNotSupported;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint32_t box[2] = {64, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+static int sm_count_tc()
+{
+    int dev = 0, n = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    return n;
+}
+
+template <int OUT_DT, int LAYOUT>
+static int launch_tc(const CUtensorMap &tw, const CUtensorMap &ty, void *C, int M, int N, int K, cudaStream_t st)
+{
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<OUT_DT, LAYOUT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         TC_SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    const int tiles = ((M + TC_BM - 1) / TC_BM) * ((N + TC_BN - 1) / TC_BN);
+    const int grid = tiles < sm_count_tc() ? tiles : sm_count_tc();
+    gemm_tc_kernel<OUT_DT, LAYOUT><<<grid, 192, TC_SMEM_BYTES, st>>>(tw, ty, C, M, N, K, status_word_ptr());
+    return (int)cudaGetLastError();
+}
+
+int launch_gemm_bf16_tcgen05(const void *Y, const void *W, void *C, int M, int N, int K, int out_dtype,
+                             int out_layout, cudaStream_t st)
+{
+    if (K < TC_BK) {
+        dim3 blk(32, 8), grd((N + 31) / 32, (M + 7) / 8);
+        gemm_bf16_smallk_kernel<<<grd, blk, 0, st>>>((const __nv_bfloat16 *)Y, (const __nv_bfloat16 *)W, C, M, N, K,
+                                                     out_dtype, out_layout);
+        return (int)cudaGetLastError();
+    }
+    CUtensorMap tw, ty;
+    int rc = encode_tmap_bf16_2d(&tw, W, (uint64_t)M, (uint64_t)K, TC_BM);
+    if (rc) return rc;
+    rc = encode_tmap_bf16_2d(&ty, Y, (uint64_t)N, (uint64_t)K, TC_BN);
+    if (rc) return rc;
+    if (out_dtype == B200HT_F32) {
+        return out_layout == B200HT_OUT_MN ? launch_tc<B200HT_F32, B200HT_OUT_MN>(tw, ty, C, M, N, K, st)
+                                           : launch_tc<B200HT_F32, B200HT_OUT_NM>(tw, ty, C, M, N, K, st);
+    }
+    return out_layout == B200HT_OUT_MN ? launch_tc<B200HT_BF16, B200HT_OUT_MN>(tw, ty, C, M, N, K, st)
+                                       : launch_tc<B200HT_BF16, B200HT_OUT_NM>(tw, ty, C, M, N, K, st);
+}
+
+}  // namespace b200ht

@@ -1,0 +1,174 @@
+"""Host-side operators: the reference's op boundary over the b200ht C ABI.
+
+``hadamard_transform(x, inplace=False)`` keeps the name, arguments, defaults,
+error messages and aliasing rules of the reference's pybind op
+(csrc/hadamard_transform.cpp:12-92).  ``fused_ht_gemm`` and ``fused_ht_gemv``
+give the reference's two fused kernels (fused_ht/fusion_pipelined.cu:306-310,
+fused_ht/fwht_gemv_fusion.cu:98-105 — launched only from ``main()`` there) a
+Python entry with the same argument order and memory layouts.
+
+PyTorch is used for device memory, streams and the caching allocator only; all
+arithmetic happens in libb200ht.so.  There is no CPU path: CPU tensors are
+rejected exactly as the reference rejects them.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _lib
+
+_DT = {torch.float16: _lib.F16, torch.bfloat16: _lib.BF16, torch.float32: _lib.F32}
+
+
+def _is_pow2(v: int) -> bool:
+    return v > 0 and (v & (v - 1)) == 0
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return int(torch.cuda.current_stream(device).cuda_stream)
+
+
+def hadamard_transform(x: torch.Tensor, inplace: bool = False, *, scale: float | None = None) -> torch.Tensor:
+    """``x @ H_n * scale`` along the last dimension, H_n in Sylvester order.
+
+    Same contract as ``csrc.hadamard_transform`` (csrc/hadamard_transform.cpp:12-70):
+    fp16/bf16 CUDA tensor of any shape whose last dimension n is a power of two
+    <= 2**15; the result has the input's shape; with ``inplace=True`` the data
+    of ``x`` is overwritten and ``x`` itself is returned, also when a temporary
+    was needed.  ``scale`` defaults to the reference's ``1/sqrt(n)``.  Unlike
+    the reference, any n >= 2 and any number of rows is accepted.
+    """
+    if x.dtype not in (torch.float16, torch.bfloat16):
+        raise RuntimeError("Only fp16 and bf16 supported currently")
+    if not x.is_cuda:
+        raise RuntimeError("Expected in.is_cuda() to be true, but got false.")
+    if x.dim() == 0:
+        raise RuntimeError("Only power of two Hadamard sizes up to 2^15 are supported, got 1")
+    n = int(x.shape[-1])
+    if not _is_pow2(n) or n > (1 << 15) or n < 2:
+        raise RuntimeError(f"Only power of two Hadamard sizes up to 2^15 are supported, got {n}")
+    if scale is None:
+        scale = math.sqrt(1.0 / n)
+
+    lib = _lib.load()
+    work = x
+    if not work.is_contiguous() or work.data_ptr() % 16 != 0:
+        work = x.contiguous()
+        if work.data_ptr() % 16 != 0:  # contiguous view at an odd storage offset
+            work = work.clone()
+    out = work if inplace else torch.empty_like(work)
+    rows = work.numel() // n
+    if rows > 0:
+        with torch.cuda.device(x.device):
+            rc = lib.b200ht_fwht(work.data_ptr(), out.data_ptr(), rows, n, _DT[x.dtype], float(scale),
+                                 _stream_ptr(x.device))
+        _lib.check(rc, "b200ht_fwht")
+    if inplace:
+        if work is not x:
+            x.copy_(out.view(x.shape))
+        return x
+    return out.view(x.shape)
+
+
+def fused_gemm_workspace_bytes(M: int, N: int, K: int, dtype: torch.dtype) -> int:
+    return int(_lib.load().b200ht_fused_gemm_workspace_bytes(M, N, K, _DT[dtype]))
+
+
+def fused_ht_gemm(X: torch.Tensor, W: torch.Tensor, *, scale: float | None = None,
+                  out_dtype: torch.dtype | None = None, out_layout: str = "mn",
+                  out: torch.Tensor | None = None, workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """C = W . H(X): ``C[m, t] = sum_k W[m, k] * (scale * H_K x_t)[k]``.
+
+    ``X`` is (N tokens, K) token-major and ``W`` is (M, K) row-major, the
+    layouts of fused_ht/fusion_pipelined.cu:148-221; argument order X, W as in
+    ``fused_ht_gemm_pipelined`` (:306-310).  Both fp32 (exact FFMA path) or
+    both bf16 (tensor cores, fp32 accumulate).  ``out_layout="mn"`` returns the
+    reference's (M, N) matrix, ``"nm"`` the token-major (N, M) one.  ``scale``
+    defaults to 1/sqrt(K); the reference executable computes ``scale=1.0``.
+    """
+    if X.dtype != W.dtype or X.dtype not in (torch.float32, torch.bfloat16):
+        raise RuntimeError("fused_ht_gemm: X and W must both be float32 or both bfloat16")
+    if not (X.is_cuda and W.is_cuda):
+        raise RuntimeError("fused_ht_gemm: X and W must be CUDA tensors")
+    if X.dim() != 2 or W.dim() != 2 or X.shape[1] != W.shape[1]:
+        raise RuntimeError("fused_ht_gemm: expected X (N, K) and W (M, K)")
+    N, K = int(X.shape[0]), int(X.shape[1])
+    M = int(W.shape[0])
+    if not _is_pow2(K) or K < 2 or K > (1 << 15):
+        raise RuntimeError(f"Only power of two Hadamard sizes up to 2^15 are supported, got {K}")
+    if out_layout not in ("mn", "nm"):
+        raise RuntimeError("fused_ht_gemm: out_layout must be 'mn' or 'nm'")
+    if scale is None:
+        scale = math.sqrt(1.0 / K)
+    out_dtype = out_dtype or torch.float32
+    if out_dtype not in (torch.float32, torch.bfloat16):
+        raise RuntimeError("fused_ht_gemm: out_dtype must be float32 or bfloat16")
+    lib = _lib.load()
+    X = X.contiguous()
+    W = W.contiguous()
+    shape = (M, N) if out_layout == "mn" else (N, M)
+    if out is None:
+        out = torch.empty(shape, dtype=out_dtype, device=X.device)
+    elif tuple(out.shape) != shape or out.dtype != out_dtype or not out.is_contiguous():
+        raise RuntimeError("fused_ht_gemm: out has the wrong shape, dtype or strides")
+    need = int(lib.b200ht_fused_gemm_workspace_bytes(M, N, K, _DT[X.dtype]))
+    if workspace is None:
+        workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=X.device)
+    elif workspace.numel() * workspace.element_size() < need:
+        raise RuntimeError("fused_ht_gemm: workspace too small")
+    if M > 0 and N > 0:
+        with torch.cuda.device(X.device):
+            rc = lib.b200ht_fused_gemm(X.data_ptr(), W.data_ptr(), out.data_ptr(), M, N, K, _DT[X.dtype],
+                                       _DT[out_dtype], _lib.OUT_MN if out_layout == "mn" else _lib.OUT_NM,
+                                       float(scale), workspace.data_ptr(),
+                                       workspace.numel() * workspace.element_size(), _stream_ptr(X.device))
+        _lib.check(rc, "b200ht_fused_gemm")
+    return out
+
+
+def fused_ht_gemv(W: torch.Tensor, X: torch.Tensor, *, scale: float | None = None,
+                  out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Y = W . H(X) for a small batch: ``Y[m, b] = sum_k W[m, k] * (scale * H_N x_b)[k]``.
+
+    ``W`` is (M, N) row-major, ``X`` is (N, B) with b fastest and the result is
+    (M, B) with b fastest — the layouts and the argument order (W, X) of
+    ``fused_hadamard_gemv_kernel`` (fused_ht/fwht_gemv_fusion.cu:98-159).
+    1 <= B <= 64.  ``scale`` defaults to 1/sqrt(N); the reference uses 1.0.
+    """
+    if X.dtype != W.dtype or X.dtype not in (torch.float32, torch.bfloat16):
+        raise RuntimeError("fused_ht_gemv: W and X must both be float32 or both bfloat16")
+    if not (X.is_cuda and W.is_cuda):
+        raise RuntimeError("fused_ht_gemv: W and X must be CUDA tensors")
+    if X.dim() == 1:
+        X = X[:, None]
+    if X.dim() != 2 or W.dim() != 2 or X.shape[0] != W.shape[1]:
+        raise RuntimeError("fused_ht_gemv: expected W (M, N) and X (N, B)")
+    M, N = int(W.shape[0]), int(W.shape[1])
+    B = int(X.shape[1])
+    if not _is_pow2(N) or N < 2 or N > (1 << 15):
+        raise RuntimeError(f"Only power of two Hadamard sizes up to 2^15 are supported, got {N}")
+    if B < 1 or B > 64:
+        raise RuntimeError(f"fused_ht_gemv: batch must be in 1..64, got {B}")
+    if scale is None:
+        scale = math.sqrt(1.0 / N)
+    out_dtype = out_dtype or torch.float32
+    lib = _lib.load()
+    X = X.contiguous()
+    W = W.contiguous()
+    if out is None:
+        out = torch.empty((M, B), dtype=out_dtype, device=W.device)
+    elif tuple(out.shape) != (M, B) or out.dtype != out_dtype or not out.is_contiguous():
+        raise RuntimeError("fused_ht_gemv: out has the wrong shape, dtype or strides")
+    if M > 0:
+        with torch.cuda.device(W.device):
+            rc = lib.b200ht_fused_gemv(W.data_ptr(), X.data_ptr(), out.data_ptr(), M, N, B, _DT[W.dtype],
+                                       _DT[out_dtype], float(scale), _stream_ptr(W.device))
+        _lib.check(rc, "b200ht_fused_gemv")
+    return out
+
+
+def device_status(clear: bool = True) -> int:
+    """0, or the error code a kernel left after a bounded wait expired."""
+    return int(_lib.load().b200ht_device_status(1 if clear else 0))

@@ -1,0 +1,114 @@
+/*
+ * b200ht — C ABI of the B200 (sm_100a) Walsh-Hadamard library.
+ *
+ * Plain pointers and sizes only; every pointer is a DEVICE pointer owned by the
+ * caller unless stated otherwise.  No function allocates or frees device
+ * memory, none synchronises the host with the device: work is enqueued on the
+ * `stream` argument (a cudaStream_t passed as void*; NULL = default stream).
+ *
+ * Return value of every launcher: 0 on success, a negative B200HT_ERR_* code
+ * for a rejected argument (nothing was launched), or a positive cudaError_t
+ * reported by the runtime at launch.  b200ht_error_string() turns any of them
+ * into text.  Nothing throws, nothing calls exit().
+ *
+ * "Reference" below is Alan-Chen99/6s894_project_2025; paths are relative to it.
+ */
+#ifndef B200HT_H
+#define B200HT_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types */
+#define B200HT_F16  0
+#define B200HT_BF16 1
+#define B200HT_F32  2
+
+/* layouts of the fused-GEMM result */
+#define B200HT_OUT_MN 0 /* C[m*N+n], M x N row-major: the reference layout     */
+#define B200HT_OUT_NM 1 /* C[n*M+m], token-major: one contiguous row per token */
+
+/* argument errors (negative) */
+#define B200HT_ERR_NULL       (-1) /* a required pointer is NULL                     */
+#define B200HT_ERR_SIZE       (-2) /* size not a power of two / out of range          */
+#define B200HT_ERR_DTYPE      (-3) /* unsupported element type combination            */
+#define B200HT_ERR_ALIGN      (-4) /* pointer not 16-byte aligned                     */
+#define B200HT_ERR_WORKSPACE  (-5) /* workspace missing or too small                  */
+#define B200HT_ERR_OVERLAP    (-6) /* in/out partially overlap                        */
+#define B200HT_ERR_DEVICE     (-7) /* current device is not compute capability 10.x   */
+#define B200HT_ERR_TIMEOUT    (-8) /* a bounded device-side wait expired (see status) */
+
+/* Library version (major*10000 + minor*100 + patch). */
+int b200ht_version(void);
+
+/* Text for a return code of any function below. Never NULL. */
+const char *b200ht_error_string(int code);
+
+/*
+ * Standalone transform: out[r, :] = scale * in[r, :] . H_n for r < rows, H_n the
+ * Sylvester-ordered Hadamard matrix of size n (a power of two, 2 <= n <= 32768).
+ * Arithmetic in fp32, one rounding to `dtype` on store.  `dtype` is B200HT_F16
+ * or B200HT_BF16 (B200HT_F32 is also accepted: exact fp32 butterflies).
+ * in == out (exactly) is allowed; partial overlap is not.  Both pointers must be
+ * 16-byte aligned.  rows may be any value >= 0 (0 is a no-op).
+ *
+ * Replaces  template<DType> void run_fht(void* a, void* out, uint32_t numel,
+ *           uint32_t had_size, cudaStream_t stream)   (csrc/main.cuh:5-6,
+ * csrc/main.cu:79-122), which the reference's op calls with scale 1/sqrt(n)
+ * baked in (csrc/hada.cuh:49-57) and which accepts only n = 2^8..2^15 and row
+ * counts divisible by its rows-per-block (csrc/main.cu:64,108).
+ */
+int b200ht_fwht(const void *in, void *out, uint64_t rows, uint32_t n, int dtype,
+                float scale, void *stream);
+
+/*
+ * Fused C = W . H(X):  C[m, t] = sum_k W[m, k] * (scale * H_K x_t)[k].
+ *   X  N x K, token-major (X[t*K + k])           in_dtype  F32 | BF16
+ *   W  M x K, row-major   (W[m*K + k])           in_dtype  (same as X)
+ *   C  M x N (B200HT_OUT_MN) or N x M (B200HT_OUT_NM), out_dtype F32 | BF16
+ * K must be a power of two, 2 <= K <= 32768.  F32 inputs are multiplied in
+ * fp32 (FFMA); BF16 inputs go through the bf16 tensor cores with fp32
+ * accumulation.  `workspace` must hold at least
+ * b200ht_fused_gemm_workspace_bytes(M, N, K, in_dtype) bytes, 256-byte
+ * aligned; it carries the transformed tokens between the two phases of the
+ * operation and is sized to stay resident in L2.  Argument order X, W, C as in
+ *   __global__ void fused_ht_gemm_pipelined(const float* X, const float* W,
+ *   float* C)   (fused_ht/fusion_pipelined.cu:306-310; dims are compile-time
+ * constants there, :51-53, and the transform is unscaled: pass scale = 1.0f to
+ * reproduce it).
+ */
+size_t b200ht_fused_gemm_workspace_bytes(int M, int N, int K, int in_dtype);
+int b200ht_fused_gemm(const void *X, const void *W, void *C, int M, int N, int K,
+                      int in_dtype, int out_dtype, int out_layout, float scale,
+                      void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * Small-batch fused Y = W . H(X):  Y[m*B + b] = sum_k W[m*N + k] * (scale * H_N x_b)[k]
+ *   W  M x N row-major, X  N x B with b fastest (X[i*B + b]), Y  M x B, b fastest.
+ * N must be a power of two, 2 <= N <= 32768; 1 <= B <= 64.  in_dtype F32 | BF16
+ * (W and X alike), out_dtype F32 | BF16.  W is streamed from HBM exactly once.
+ * Argument order W, X, Y, M, N, B as in
+ *   __global__ void fused_hadamard_gemv_kernel(const float* W, const float* X,
+ *   float* Y, int M, int N, int B)   (fused_ht/fwht_gemv_fusion.cu:98-105; the
+ * float4 variant :176-183 has the same signature).  The reference is unscaled:
+ * pass scale = 1.0f to reproduce it.
+ */
+int b200ht_fused_gemv(const void *W, const void *X, void *Y, int M, int N, int B,
+                      int in_dtype, int out_dtype, float scale, void *stream);
+
+/*
+ * Device-side status word of the calling thread's current device: 0, or the
+ * B200HT_ERR_TIMEOUT code left by a kernel whose bounded wait on an mbarrier
+ * expired.  Synchronises the device.  `clear` != 0 resets it.  The reference has
+ * no counterpart (its kernels have no waits that can expire).
+ */
+int b200ht_device_status(int clear);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200HT_H */

@@ -1,0 +1,156 @@
+"""GPU parity of the fused W . H(X) entry points against the CPU oracle.
+Tolerances from the task statement: relative error <= 1e-5 for fp32, <= 2e-2
+for bf16 inputs with fp32 accumulation (both as ||.||_F ratio and max ratio)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+F32_TOL = 1e-5
+BF16_TOL = 2e-2
+
+
+def _check(oracle, got, ref, tol):
+    got = np.asarray(got, dtype=np.float64)
+    assert oracle.rel_fro(got, ref) <= tol, oracle.rel_fro(got, ref)
+    assert oracle.rel_max(got, ref) <= tol, oracle.rel_max(got, ref)
+
+
+def test_c1_fp32_gemv(pkg, oracle):
+    inp = oracle.make_inputs("c1")
+    W, X = inp["W"], inp["X"]
+    ref = oracle.fused_gemv_ref(W.numpy(), X.numpy())
+    Y = pkg.fused_ht_gemv(W.cuda(), X.cuda())
+    assert Y.shape == (32, 8)
+    _check(oracle, Y.cpu().numpy(), ref, F32_TOL)
+    # the same numbers through the GEMM entry (tokens = columns of X)
+    C = pkg.fused_ht_gemm(X.t().contiguous().cuda(), W.cuda())
+    _check(oracle, C.cpu().numpy(), ref, F32_TOL)
+
+
+def test_golden_fused_vectors(pkg, oracle, golden):
+    g = golden["fused"]
+    W, X, Y = map(torch.from_numpy, (g["c1_W"], g["c1_X"], g["c1_Y"]))
+    got = pkg.fused_ht_gemv(W.cuda(), X.cuda()).cpu().numpy()
+    _check(oracle, got, Y.numpy(), 2e-5)   # the golden itself is an fp32 computation
+    Xg, Wg, Cg = map(torch.from_numpy, (g["g_X"], g["g_W"], g["g_C"]))
+    got = pkg.fused_ht_gemm(Xg.cuda(), Wg.cuda()).cpu().numpy()
+    _check(oracle, got, Cg.numpy(), 2e-5)
+    got = pkg.fused_ht_gemm(Xg.cuda(), Wg.cuda(), out_layout="nm").cpu().numpy()
+    _check(oracle, got.T, Cg.numpy(), 2e-5)
+
+
+@pytest.mark.parametrize("M,N,K", [(32, 8, 64), (1, 1, 2), (7, 5, 4), (130, 67, 16), (128, 256, 128),
+                                   (300, 129, 1024), (64, 33, 8192)])
+def test_fp32_gemm_shapes(pkg, oracle, M, N, K):
+    inp = oracle.make_inputs("c3", K=K, N=N, M=M)
+    X, W = inp["X"], inp["W"]
+    ref = oracle.fused_gemm_ref(X.numpy(), W.numpy())
+    for layout in ("mn", "nm"):
+        C = pkg.fused_ht_gemm(X.cuda(), W.cuda(), out_layout=layout).cpu().numpy()
+        _check(oracle, C if layout == "mn" else C.T, ref, F32_TOL)
+    # reference executable convention: unscaled transform
+    ref1 = oracle.fused_gemm_ref(X.numpy(), W.numpy(), scale=1.0)
+    C = pkg.fused_ht_gemm(X.cuda(), W.cuda(), scale=1.0).cpu().numpy()
+    _check(oracle, C, ref1, F32_TOL)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 128), (256, 512, 256), (100, 77, 64),
+                                   (129, 257, 1024), (384, 300, 4096), (8, 4, 32), (5, 3, 2),
+                                   (2048, 1024, 2048)])
+def test_bf16_gemm_shapes(pkg, oracle, M, N, K):
+    inp = oracle.make_inputs("c3", K=K, N=N, M=M)
+    X, W = inp["X"].bfloat16(), inp["W"].bfloat16()
+    ref = oracle.fused_gemm_ref(X.double().numpy(), W.double().numpy())
+    for layout, odt in (("mn", torch.float32), ("nm", torch.float32), ("mn", torch.bfloat16), ("nm", torch.bfloat16)):
+        C = pkg.fused_ht_gemm(X.cuda(), W.cuda(), out_layout=layout, out_dtype=odt)
+        assert pkg.device_status() == 0
+        C = C.float().cpu().numpy()
+        _check(oracle, C if layout == "mn" else C.T, ref, BF16_TOL)
+
+
+def test_c3_full_size_fp32_and_bf16(pkg, oracle):
+    inp = oracle.make_inputs("c3")
+    X, W = inp["X"], inp["W"]                       # 4096 x 1024 each
+    rows = np.array([0, 1, 127, 128, 2047, 4095])
+    Y = oracle.fwht_rows(X.double().numpy())        # 4096 x 1024
+    ref_rows = W.double().numpy()[rows] @ Y.T       # 6 x 4096
+    C = pkg.fused_ht_gemm(X.cuda(), W.cuda())
+    _check(oracle, C[rows].cpu().numpy(), ref_rows, F32_TOL)
+    Xb, Wb = X.bfloat16(), W.bfloat16()
+    Yb = oracle.fwht_rows(Xb.double().numpy())
+    refb = Wb.double().numpy()[rows] @ Yb.T
+    Cb = pkg.fused_ht_gemm(Xb.cuda(), Wb.cuda())
+    assert pkg.device_status() == 0
+    _check(oracle, Cb[rows].cpu().numpy(), refb, BF16_TOL)
+    # checksum of checksums: column sums of C equal (sum of W rows) . H(X)
+    colsum = Cb.double().sum(dim=0).cpu().numpy()
+    ref_colsum = Wb.double().numpy().sum(axis=0) @ Yb.T
+    assert oracle.rel_fro(colsum, ref_colsum) <= BF16_TOL
+
+
+@pytest.mark.parametrize("B", [1, 4, 16])
+def test_c4_bf16_gemv(pkg, oracle, B):
+    inp = oracle.make_inputs("c4", B=B)
+    W, X = inp["W"], inp["X"]
+    ref = oracle.fused_gemv_ref(W.double().numpy(), X.double().numpy())
+    Y = pkg.fused_ht_gemv(W.cuda(), X.cuda())
+    assert Y.shape == (4096, B)
+    _check(oracle, Y.cpu().numpy(), ref, BF16_TOL)
+    Yb = pkg.fused_ht_gemv(W.cuda(), X.cuda(), out_dtype=torch.bfloat16)
+    _check(oracle, Yb.float().cpu().numpy(), ref, BF16_TOL)
+
+
+@pytest.mark.parametrize("M,N,B,dtype", [(32, 64, 8, torch.float32), (64, 128, 16, torch.float32),
+                                         (128, 256, 32, torch.float32), (5, 2, 1, torch.float32),
+                                         (33, 32, 3, torch.bfloat16), (100, 512, 9, torch.bfloat16),
+                                         (17, 2048, 64, torch.bfloat16), (40, 32768, 2, torch.bfloat16),
+                                         (9, 16384, 5, torch.float32)])
+def test_gemv_shapes_including_reference_self_tests(pkg, oracle, M, N, B, dtype):
+    # (32,64,8), (64,128,16), (128,256,32) are the shapes of fwht_gemv_fusion.cu:632-634;
+    # inputs uniform in [-1, 1] and the unscaled transform, as there (:278-282)
+    g = torch.Generator().manual_seed(42)
+    W = (torch.rand(M, N, generator=g) * 2 - 1).to(dtype)
+    X = (torch.rand(N, B, generator=g) * 2 - 1).to(dtype)
+    ref = oracle.fused_gemv_ref(W.double().numpy(), X.double().numpy(), scale=1.0)
+    Y = pkg.fused_ht_gemv(W.cuda(), X.cuda(), scale=1.0).cpu().numpy()
+    tol = F32_TOL if dtype == torch.float32 else BF16_TOL
+    _check(oracle, Y, ref, tol)
+    if dtype == torch.float32 and N <= 256:
+        assert np.max(np.abs(Y - ref)) < 1e-3   # the reference's own absolute gate (:293-312)
+
+
+def test_c5_reduced_and_sharded(pkg, oracle):
+    """C5 distribution at a reduced shape; 2-way and 4-way token shards must
+    reproduce the unsharded result bit for bit."""
+    inp = oracle.make_inputs("c5", K=8192, M=512, N=768)
+    X, W = inp["X"], inp["W"]
+    ref = oracle.fused_gemm_ref(X.double().numpy(), W.double().numpy())
+    Xd, Wd = X.cuda(), W.cuda()
+    full = pkg.fused_ht_gemm(Xd, Wd, out_layout="nm")
+    assert pkg.device_status() == 0
+    _check(oracle, full.cpu().numpy().T, ref, BF16_TOL)
+    for world in (2, 4):
+        parts = [pkg.fused_ht_gemm(pkg.shard_tokens(Xd, r, world), Wd, out_layout="nm") for r in range(world)]
+        assert torch.equal(torch.cat(parts, dim=0), full)
+
+
+def test_c5_full_size_sampled(pkg, oracle):
+    inp = oracle.make_inputs("c5")
+    X, W = inp["X"], inp["W"]                        # 16384 x 8192, 28672 x 8192
+    Xd, Wd = X.cuda(), W.cuda()
+    C = pkg.fused_ht_gemm(Xd, Wd, out_layout="nm", out_dtype=torch.bfloat16)   # 16384 x 28672
+    assert pkg.device_status() == 0
+    toks = np.array([0, 255, 256, 8191, 12345, 16383])
+    rows = np.array([0, 127, 128, 14335, 20000, 28671])
+    Y = oracle.fwht_rows(X[toks].double().numpy())            # 6 x 8192
+    ref = Y @ W[rows].double().numpy().T                      # 6 tokens x 6 rows
+    got = C[toks][:, rows].float().cpu().numpy()
+    _check(oracle, got, ref, BF16_TOL)
+    # checksum over all rows of W for the sampled tokens
+    ref_sum = Y @ W.double().numpy().sum(axis=0)
+    got_sum = C[toks].double().sum(dim=1).cpu().numpy()
+    assert oracle.rel_fro(got_sum, ref_sum) <= BF16_TOL

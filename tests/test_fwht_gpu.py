@@ -1,0 +1,137 @@
+"""GPU parity of the standalone transform against the CPU oracle, through the
+Python op (which calls the C ABI).  Tolerances: the reference's own absolute
+tolerances, atol 1e-2 (fp16) / 5e-2 (bf16), rtol 0 (HadaCore/test.py:93,99;
+bench/bench.py:261-264), plus a relative Frobenius bound of 2e-2 for bf16 and
+4e-3 for fp16."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [(torch.float16, 1e-2, 4e-3), (torch.bfloat16, 5e-2, 2e-2)]
+
+
+def _ref(oracle, x16: torch.Tensor) -> np.ndarray:
+    return oracle.fwht_rows(x16.double().cpu().numpy())
+
+
+@pytest.mark.parametrize("logn", range(1, 16))
+@pytest.mark.parametrize("dtype,atol,rfro", DTYPES)
+def test_all_sizes_ragged_rows(pkg, oracle, logn, dtype, atol, rfro):
+    n = 1 << logn
+    g = torch.Generator().manual_seed(100 + logn)
+    for rows in (1, 3, 5, 37):
+        x = torch.randn(rows, n, generator=g).to(dtype)
+        y = pkg.hadamard_transform(x.cuda())
+        assert y.shape == x.shape and y.dtype == dtype
+        ref = _ref(oracle, x)
+        got = y.double().cpu().numpy()
+        assert np.max(np.abs(got - ref)) <= atol, (n, rows)
+        assert oracle.rel_fro(got, ref) <= rfro
+
+
+@pytest.mark.parametrize("logn", range(1, 13))
+def test_against_reference_golden_vectors(pkg, golden, logn):
+    n = 1 << logn
+    g = golden["fwht"]
+    x = torch.from_numpy(g[f"x_{n}"])
+    for key, dt, atol in (("yf16", torch.float16, 1e-2), ("yb16", torch.bfloat16, 5e-2)):
+        y = pkg.hadamard_transform(x.to(dt).cuda()).float().cpu().numpy()
+        # the golden output is the reference's 16-bit matmul; both sit within atol of the exact result
+        assert np.max(np.abs(y - g[f"{key}_{n}"])) <= 2 * atol
+        assert np.max(np.abs(y - g[f"y32_{n}"])) <= atol + 4e-2  # input cast + output rounding
+
+
+@pytest.mark.parametrize("n", [2, 8, 64, 256, 1024, 4096, 32768])
+def test_known_answers(pkg, n):
+    # all-ones row -> sqrt(n) * e_0 ; unit spike at j -> row j of H / sqrt(n)
+    ones = torch.ones(2, n, dtype=torch.float16, device="cuda")
+    y = pkg.hadamard_transform(ones).float().cpu()
+    assert abs(y[0, 0].item() - n ** 0.5) <= 1e-2 * n ** 0.5 and y[0, 1:].abs().max().item() <= 1e-3
+    js = sorted({0, 1, n // 2, n - 1, (n * 5) // 8})
+    e = torch.zeros(len(js), n, dtype=torch.float16)
+    for r, j in enumerate(js):
+        e[r, j] = 1.0
+    y = pkg.hadamard_transform(e.cuda(), scale=1.0).float().cpu().numpy()
+    idx = np.arange(n)
+    for r, j in enumerate(js):
+        sign = 1 - 2 * (np.array([bin(j & i).count("1") for i in idx]) & 1)
+        assert np.array_equal(y[r], sign.astype(np.float32)), (n, j)
+
+
+@pytest.mark.parametrize("n", [16, 256, 2048, 8192])
+def test_inplace_and_aliasing_rules(pkg, oracle, n):
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(6, n, generator=g).bfloat16()
+    ref = _ref(oracle, x)
+    xd = x.cuda()
+    before = xd.clone()
+    y = pkg.hadamard_transform(xd)
+    assert torch.equal(xd, before), "out-of-place call modified its input"
+    r = pkg.hadamard_transform(xd, inplace=True)
+    assert r is xd and torch.equal(xd, y)
+    assert np.max(np.abs(xd.double().cpu().numpy() - ref)) <= 5e-2
+    # non-contiguous input (a column slice): still correct, and inplace writes through the view
+    big = torch.randn(6, 2 * n, generator=g).bfloat16().cuda()
+    view = big[:, :n]
+    refv = _ref(oracle, view.cpu())
+    out = pkg.hadamard_transform(view)
+    assert np.max(np.abs(out.double().cpu().numpy() - refv)) <= 5e-2
+    keep = big[:, n:].clone()
+    r = pkg.hadamard_transform(view, inplace=True)
+    assert r is view and torch.equal(big[:, :n], out) and torch.equal(big[:, n:], keep)
+
+
+def test_higher_rank_and_empty(pkg, oracle):
+    x = torch.randn(2, 3, 5, 128, generator=torch.Generator().manual_seed(1)).half()
+    y = pkg.hadamard_transform(x.cuda())
+    assert y.shape == x.shape
+    assert np.max(np.abs(y.double().cpu().numpy() - _ref(oracle, x))) <= 1e-2
+    e = torch.empty(0, 64, dtype=torch.bfloat16, device="cuda")
+    assert pkg.hadamard_transform(e).shape == (0, 64)
+    with pytest.raises(RuntimeError, match="Only power of two"):
+        pkg.hadamard_transform(torch.zeros(2, 48, dtype=torch.float16, device="cuda"))
+    with pytest.raises(RuntimeError, match="Only power of two"):
+        pkg.hadamard_transform(torch.zeros(2, 1 << 16, dtype=torch.float16, device="cuda"))
+
+
+@pytest.mark.parametrize("logn", [8, 11, 12, 15])
+def test_full_size_properties(pkg, logn):
+    """16384 x n (the benchmark shape): involution, linearity and energy
+    preservation, checked on the device (the oracle cannot afford this size)."""
+    n = 1 << logn
+    g = torch.Generator(device="cuda").manual_seed(logn)
+    x = torch.randn(16384, n, generator=g, device="cuda").bfloat16()
+    y = pkg.hadamard_transform(x)
+    back = pkg.hadamard_transform(y)
+    err = (back.float() - x.float()).norm() / x.float().norm()
+    assert err.item() < 1.5e-2
+    e_in = x.float().pow(2).sum(dim=1)
+    e_out = y.float().pow(2).sum(dim=1)
+    assert ((e_out - e_in).abs() / e_in).max().item() < 2e-2
+    # linearity: H(a) + H(b) ~= H(a + b) for exactly representable sums
+    a = (torch.randint(-8, 9, (64, n), generator=g, device="cuda")).bfloat16()
+    b = (torch.randint(-8, 9, (64, n), generator=g, device="cuda")).bfloat16()
+    lhs = pkg.hadamard_transform(a).float() + pkg.hadamard_transform(b).float()
+    rhs = pkg.hadamard_transform(a + b).float()
+    assert (lhs - rhs).abs().max().item() <= 0.13 * (n ** 0.5) / 16 + 0.26
+    # a slab of rows against the oracle
+    import importlib
+    oracle = importlib.import_module("oracle.fwht_oracle")
+    rows = [0, 1, 8191, 16383]
+    ref = oracle.fwht_rows(x[rows].double().cpu().numpy())
+    assert np.max(np.abs(y[rows].double().cpu().numpy() - ref)) <= 5e-2
+
+
+def test_fp32_entry_is_exact_to_fp32(pkg, lib, oracle):
+    l = lib.load()
+    for n in (2, 64, 1024, 4096, 32768):
+        x = torch.randn(5, n, generator=torch.Generator().manual_seed(n))
+        xd = x.cuda()
+        out = torch.empty_like(xd)
+        rc = l.b200ht_fwht(xd.data_ptr(), out.data_ptr(), 5, n, lib.F32, float(n ** -0.5),
+                           torch.cuda.current_stream().cuda_stream)
+        assert rc == 0, lib.error_string(rc)
+        ref = oracle.fwht_rows(x.double().numpy())
+        assert oracle.rel_fro(out.cpu().numpy(), ref) <= 1e-6
