@@ -18,6 +18,7 @@ no collective on the data path), so total work is fixed: strong scaling.
             GEMM kernel alone) against the measured sustained bf16 peak
   fwht      secondary block: standalone transform of (16384, n) bf16, n = 2^8..
             2^15, HBM GB/s against the measured copy bandwidth
+  gemv      secondary block: fused GEMV, W 4096 x 4096 bf16, B = 1, 4, 16, GB/s
   cpu_baseline  the reference's torch path (explicit Hadamard matmul, then
             matmul; bench/bench.py:44-59 of the reference) on the host cores,
             on a bounded slice of the same tokens
@@ -43,6 +44,7 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 K_DIM, M_DIM, N_TOKENS = 8192, 28672, 16384
+CPU_SAMPLE_TOKENS = 4096  # bounded slice for the CPU legs: ~1-2 s of host work per step
 METRIC = "fused W.H(X) TFLOP/s (K=8192, M=28672, 16384 tokens, bf16 in / fp32 acc); FWHT HBM GB/s in 'fwht'"
 
 
@@ -132,7 +134,7 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    tokens = 256
+    tokens = CPU_SAMPLE_TOKENS
     X, W, H = cpu_setup(tokens)
     for _ in range(max(args.warmup, 1)):
         cpu_reference_step(X, W, H)
@@ -192,6 +194,42 @@ def time_fwht_sweep(pkg, torch, peaks, rows=16384, reps=10):
         gbs = rows * n * 4 / (ms * 1e-3) / 1e9
         out[str(n)] = {"ms": ms, "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"]}
         del bufs, dst
+    return out
+
+
+def time_gemv(pkg, torch, peaks, reps=20):
+    """Small-batch fused GEMV, W 4096 x 4096 bf16, B in {1, 4, 16}.  W (33.5 MB)
+    would sit in L2, so 16 copies are rotated (537 MB per rotation)."""
+    M = N = 4096
+    out = {}
+    g = torch.Generator(device="cuda").manual_seed(3)
+    Ws = [(torch.randn(M, N, generator=g, device="cuda") / 64).bfloat16() for _ in range(16)]
+    lib = pkg._lib.load()
+    st = torch.cuda.current_stream().cuda_stream
+    for B in (1, 4, 16):
+        X = torch.randn(N, B, generator=g, device="cuda").bfloat16()
+        Y = torch.empty(M, B, dtype=torch.float32, device="cuda")
+
+        def call(Wt):
+            rc = lib.b200ht_fused_gemv(Wt.data_ptr(), X.data_ptr(), Y.data_ptr(), M, N, B, pkg._lib.BF16,
+                                       pkg._lib.F32, float(N ** -0.5), st)
+            if rc:
+                raise RuntimeError(pkg._lib.error_string(rc))
+
+        for Wt in Ws[:3]:
+            call(Wt)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            for Wt in Ws:
+                call(Wt)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / (reps * len(Ws))
+        nbytes = M * N * 2 + N * B * 2 + M * B * 4
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[str(B)] = {"ms": ms, "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"]}
     return out
 
 
@@ -279,6 +317,7 @@ def run_gpu_arm(args):
     e2e_val = flops_total / (e2e_ms * 1e-3) / 1e12
 
     fwht = time_fwht_sweep(pkg, torch, peaks)
+    gemv = time_gemv(pkg, torch, peaks)
     if world > 1:
         agg = torch.tensor([fwht[k]["gbs"] for k in sorted(fwht, key=int)], device="cuda")
         dist.all_reduce(agg, op=dist.ReduceOp.SUM)
@@ -289,7 +328,7 @@ def run_gpu_arm(args):
         cpu = None
         if world == 1:
             import torch as _t
-            tokens = 256
+            tokens = CPU_SAMPLE_TOKENS
             Xc, Wc, Hc = cpu_setup(tokens)
             cpu_reference_step(Xc, Wc, Hc)
             best = 1e30
@@ -320,6 +359,7 @@ def run_gpu_arm(args):
                               "frac": best_fwht["gbs"] / peaks["hbm_gbs"], "traffic": None,
                               "peak_source": f"{peaks['source']} copy bandwidth"},
             "fwht": fwht,
+            "gemv": gemv,
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": X.numel() * 2 * world, "d2h_bytes_per_step": C.numel() * 2 * world},
