@@ -14,6 +14,7 @@ LIB_PATH = _HERE / "libb200ht.so"
 
 F16, BF16, F32 = 0, 1, 2
 OUT_MN, OUT_NM = 0, 1
+STATIC_SCRATCH_BYTES = 32 << 20
 
 # every symbol include/b200ht.h declares
 EXPORTS = (
@@ -22,6 +23,7 @@ EXPORTS = (
     "b200ht_fwht",
     "b200ht_fused_gemm_workspace_bytes",
     "b200ht_fused_gemm",
+    "b200ht_fused_gemm_static",
     "b200ht_fused_gemv",
     "b200ht_device_status",
 )
@@ -42,6 +44,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.b200ht_fused_gemm_workspace_bytes.argtypes = [i, i, i, i]
     lib.b200ht_fused_gemm.restype = i
     lib.b200ht_fused_gemm.argtypes = [vp, vp, vp, i, i, i, i, i, i, f, vp, ctypes.c_size_t, vp]
+    lib.b200ht_fused_gemm_static.restype = i
+    lib.b200ht_fused_gemm_static.argtypes = [vp, vp, vp, i, i, i, i, i, i, f, vp]
     lib.b200ht_fused_gemv.restype = i
     lib.b200ht_fused_gemv.argtypes = [vp, vp, vp, i, i, i, i, i, f, vp]
     lib.b200ht_device_status.restype = i

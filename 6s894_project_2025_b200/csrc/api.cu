@@ -48,6 +48,9 @@ extern "C" const char *b200ht_error_string(int code)
     case B200HT_ERR_OVERLAP: return "b200ht: input and output partially overlap";
     case B200HT_ERR_DEVICE: return "b200ht: current device is not an sm_100 (B200) GPU";
     case B200HT_ERR_TIMEOUT: return "b200ht: a bounded device-side wait expired";
+    case B200HT_ERR_STATIC_SCRATCH:
+        return "b200ht: problem too large for the built-in static scratch (B200HT_STATIC_SCRATCH_BYTES); "
+               "split the tokens or pass a workspace to b200ht_fused_gemm";
     default: break;
     }
     if (code > 0) return cudaGetErrorString((cudaError_t)code);

@@ -5,6 +5,8 @@
 // stay L2-resident, followed on the same stream by the contraction against W.
 //   fp32 inputs: exact fp32 butterflies + FFMA GEMM (sgemm_nt_kernel, this file)
 //   bf16 inputs: 16-bit transform (fwht.cu) + tcgen05 GEMM (gemm_tcgen05.cu)
+#include <mutex>
+
 #include "common.cuh"
 
 namespace b200ht {
@@ -176,4 +178,66 @@ extern "C" int b200ht_fused_gemm(const void *X, const void *W, void *C, int M, i
     if (in_dtype == B200HT_F32)
         return launch_sgemm((const float *)W, (const float *)workspace, C, M, N, K, out_dtype, out_layout, st);
     return launch_gemm_bf16_tcgen05(workspace, W, C, M, N, K, out_dtype, out_layout, st);
+}
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant of b200ht_fused_gemm.
+//
+// Some callers cannot hand this library a workspace because they cannot
+// allocate one at the point of the call: a serving process whose own pool took
+// all device memory at start-up, a plugin whose enqueue hook is forbidden to
+// allocate, a latency-critical loop that must not take the driver's allocation
+// lock (cudaMalloc may also synchronise the device).  For them the transformed
+// tokens go into a fixed array that is part of the library image.
+//
+// g_static_scratch is a __device__ array: in host code its name is only a
+// handle for the runtime, not a device address.  The address the kernels and
+// the TMA descriptor need is resolved with cudaGetSymbolAddress, once per
+// device, while that device is current.
+// ---------------------------------------------------------------------------
+namespace b200ht {
+
+static __device__ __align__(256) unsigned char g_static_scratch[B200HT_STATIC_SCRATCH_BYTES];
+
+static int static_scratch_address(void **out)
+{
+    static std::mutex mu;
+    static void *addr[64] = {nullptr};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return B200HT_ERR_DEVICE;
+    std::lock_guard<std::mutex> lk(mu);
+    if (!addr[dev]) {
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        if (!p) return B200HT_ERR_NULL;
+        addr[dev] = p;
+    }
+    *out = addr[dev];
+    return 0;
+}
+
+}  // namespace b200ht
+
+extern "C" int b200ht_fused_gemm_static(const void *X, const void *W, void *C, int M, int N, int K, int in_dtype,
+                                        int out_dtype, int out_layout, float scale, void *stream)
+{
+    using namespace b200ht;
+    if (in_dtype != B200HT_F32 && in_dtype != B200HT_BF16) return B200HT_ERR_DTYPE;
+    if (M < 0 || N < 0 || K < 2) return B200HT_ERR_SIZE;
+    // Reject before anything is enqueued: the transformed tokens must fit the built-in array.
+    const size_t need = b200ht_fused_gemm_workspace_bytes(M, N, K, in_dtype);
+    if (need > (size_t)B200HT_STATIC_SCRATCH_BYTES) return B200HT_ERR_STATIC_SCRATCH;
+    int rc = check_device();
+    if (rc) return rc;
+    void *scratch = nullptr;
+    rc = static_scratch_address(&scratch);
+    if (rc) return rc;
+    // Same two phases as b200ht_fused_gemm, on the resolved device address.  Every row of the
+    // scratch that the contraction reads is written by the transform phase of this same call,
+    // so nothing has to be cleared between calls.
+    return b200ht_fused_gemm(X, W, C, M, N, K, in_dtype, out_dtype, out_layout, scale, scratch,
+                             (size_t)B200HT_STATIC_SCRATCH_BYTES, stream);
 }

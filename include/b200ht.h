@@ -41,6 +41,7 @@ extern "C" {
 #define B200HT_ERR_OVERLAP    (-6) /* in/out partially overlap                        */
 #define B200HT_ERR_DEVICE     (-7) /* current device is not compute capability 10.x   */
 #define B200HT_ERR_TIMEOUT    (-8) /* a bounded device-side wait expired (see status) */
+#define B200HT_ERR_STATIC_SCRATCH (-9) /* problem exceeds B200HT_STATIC_SCRATCH_BYTES       */
 
 /* Library version (major*10000 + minor*100 + patch). */
 int b200ht_version(void);
@@ -85,6 +86,38 @@ size_t b200ht_fused_gemm_workspace_bytes(int M, int N, int K, int in_dtype);
 int b200ht_fused_gemm(const void *X, const void *W, void *C, int M, int N, int K,
                       int in_dtype, int out_dtype, int out_layout, float scale,
                       void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * b200ht_fused_gemm without a caller-provided workspace and without any
+ * allocation.  No counterpart in the reference (its program allocates all its
+ * buffers with cudaMalloc in main()).
+ *
+ * For callers that cannot allocate device memory where they call from: a
+ * process whose own memory pool reserved the whole GPU at start-up, a plugin
+ * whose execute hook must not allocate, a latency-critical loop that must
+ * never take the driver's allocation lock.  The transformed tokens live in a
+ * fixed B200HT_STATIC_SCRATCH_BYTES array inside the library image (each GPU
+ * that loads the library holds that much memory until the process exits).
+ *
+ * Limits and rules:
+ *  - N*K*sizeof(input element), rounded up to 256, must not exceed
+ *    B200HT_STATIC_SCRATCH_BYTES (e.g. 2048 tokens at K=8192 bf16); larger
+ *    problems return B200HT_ERR_STATIC_SCRATCH and launch nothing.  Split the
+ *    tokens into several calls, or use b200ht_fused_gemm.
+ *  - The function calls no cudaMalloc/cudaFree and no allocating library
+ *    routine.  Its first call on a device resolves the device address of the
+ *    array (cudaGetSymbolAddress) and caches it; make that first call during
+ *    set-up, before any stream capture is started.
+ *  - All calls on one device share the array, and it keeps the previous call's
+ *    contents (nothing needs clearing: each call overwrites what it reads).
+ *    Two calls whose kernels may run at the same time on one GPU (different
+ *    streams, different threads) race on it: serialise them.
+ * Other arguments, layouts and return codes: as b200ht_fused_gemm.
+ */
+#define B200HT_STATIC_SCRATCH_BYTES (32u << 20)
+int b200ht_fused_gemm_static(const void *X, const void *W, void *C, int M, int N, int K,
+                             int in_dtype, int out_dtype, int out_layout, float scale,
+                             void *stream);
 
 /*
  * Small-batch fused Y = W . H(X):  Y[m*B + b] = sum_k W[m*N + k] * (scale * H_N x_b)[k]
