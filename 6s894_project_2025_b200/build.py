@@ -30,6 +30,7 @@ NVCC_FLAGS = [
     "-O3", "-std=c++17", "-lineinfo",
     "-Xcompiler", "-fPIC",
     "--expt-relaxed-constexpr",
+    *(["-DB200HT_GEMV_TRACE"] if os.environ.get("B200HT_GEMV_TRACE") else []),  # developer timing hooks
     "-I", str(ROOT / "include"),
 ]
 

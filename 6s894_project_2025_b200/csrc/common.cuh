@@ -84,13 +84,13 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
                                          uint32_t b1)
 {
     if constexpr (DT == B200HT_BF16) {
-        asm volatile(
+        asm(
             "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
             "{%8,%9}, {%10,%10,%10,%10};\n"
             : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
             : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
     } else {
-        asm volatile(
+        asm(
             "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
             "{%8,%9}, {%10,%10,%10,%10};\n"
             : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
@@ -102,7 +102,7 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
 __device__ __forceinline__ void mma16816_bf16_acc(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                                   uint32_t a3, uint32_t b0, uint32_t b1)
 {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
         "{%8,%9}, {%0,%1,%2,%3};\n"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
@@ -152,6 +152,39 @@ __device__ __forceinline__ void rot8(const uint32_t (&v)[4], float (&o)[8], cons
     mma16816<DT>(d1, A2, p01, p11);
     o[0] = d0[0]; o[1] = d0[1]; o[2] = d1[0]; o[3] = d1[1];
     o[4] = d0[2]; o[5] = d0[3]; o[6] = d1[2]; o[7] = d1[3];
+}
+
+// rot8 on CNT independent chunks at once, written stage by stage so that the
+// 2*CNT mma of a stage are independent and their latencies overlap.
+template <int DT, int CNT>
+__device__ __forceinline__ void rot8x(const uint4 (&v)[CNT], float (&o)[CNT][8], const uint32_t (&A1)[4],
+                                      const uint32_t (&A2)[4])
+{
+    float c[CNT][2][4];
+#pragma unroll
+    for (int i = 0; i < CNT; ++i) {
+        mma16816<DT>(c[i][0], A1, v[i].x, v[i].y);
+        mma16816<DT>(c[i][1], A1, v[i].z, v[i].w);
+    }
+    uint32_t p[CNT][4];
+#pragma unroll
+    for (int i = 0; i < CNT; ++i) {
+        p[i][0] = pack2<DT>(c[i][0][0], c[i][0][1]);
+        p[i][1] = pack2<DT>(c[i][0][2], c[i][0][3]);
+        p[i][2] = pack2<DT>(c[i][1][0], c[i][1][1]);
+        p[i][3] = pack2<DT>(c[i][1][2], c[i][1][3]);
+    }
+    float d[CNT][2][4];
+#pragma unroll
+    for (int i = 0; i < CNT; ++i) {
+        mma16816<DT>(d[i][0], A2, p[i][0], p[i][2]);
+        mma16816<DT>(d[i][1], A2, p[i][1], p[i][3]);
+    }
+#pragma unroll
+    for (int i = 0; i < CNT; ++i) {
+        o[i][0] = d[i][0][0]; o[i][1] = d[i][0][1]; o[i][2] = d[i][1][0]; o[i][3] = d[i][1][1];
+        o[i][4] = d[i][0][2]; o[i][5] = d[i][0][3]; o[i][6] = d[i][1][2]; o[i][7] = d[i][1][3];
+    }
 }
 
 // Hadamard masks of rot8 for a transform over the low `p` (<= 8) index bits.

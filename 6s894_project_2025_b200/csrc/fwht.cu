@@ -45,11 +45,7 @@ __global__ void __launch_bounds__(256) fwht_reg_kernel(const uint4 *in, uint4 *o
         v[g] = idx < total_vec ? ld_stream(in + idx) : make_uint4(0, 0, 0, 0);
     }
     float o[GRP][8];
-#pragma unroll
-    for (int g = 0; g < GRP; ++g) {
-        const uint32_t w[4] = {v[g].x, v[g].y, v[g].z, v[g].w};
-        rot8<DT>(w, o[g], A1, A2);
-    }
+    rot8x<DT, GRP>(v, o, A1, A2);
     // index bits 8.. : butterflies across the chunks of a row, fp32
 #pragma unroll
     for (int s = 1; s < CPR; s <<= 1) {
@@ -124,20 +120,19 @@ __global__ void __launch_bounds__(256) fwht_smem_kernel(const uint4 *in, uint4 *
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int c = c0 + 8 * u;
-            if (c < chunks_here) v[u] = ld_stream(gin + c * 32 + lane);
+            v[u] = c < chunks_here ? ld_stream(gin + c * 32 + lane) : make_uint4(0, 0, 0, 0);
         }
+        float o[U][8];
+        rot8x<DT, U>(v, o, A1, A2);
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int c = c0 + 8 * u;
             if (c < chunks_here) {
-                const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-                float o[8];
-                rot8<DT>(w, o, A1, A2);
                 uint4 r;
-                r.x = pack2<DT>(o[0], o[1]);
-                r.y = pack2<DT>(o[2], o[3]);
-                r.z = pack2<DT>(o[4], o[5]);
-                r.w = pack2<DT>(o[6], o[7]);
+                r.x = pack2<DT>(o[u][0], o[u][1]);
+                r.y = pack2<DT>(o[u][2], o[u][3]);
+                r.z = pack2<DT>(o[u][4], o[u][5]);
+                r.w = pack2<DT>(o[u][6], o[u][7]);
                 sm[c * 33 + lane] = r;
             }
         }
@@ -160,12 +155,10 @@ __global__ void __launch_bounds__(256) fwht_smem_kernel(const uint4 *in, uint4 *
             chunk0 = (item >> 4) * CPR + (lane & 15);
         }
         float o[J][8];
+        uint4 tv[J];
 #pragma unroll
-        for (int j = 0; j < J; ++j) {
-            const uint4 t = sm[(chunk0 + 32 * j) * 33 + slot];
-            const uint32_t w[4] = {t.x, t.y, t.z, t.w};
-            rot8<DT>(w, o[j], A1, A2);
-        }
+        for (int j = 0; j < J; ++j) tv[j] = sm[(chunk0 + 32 * j) * 33 + slot];
+        rot8x<DT, J>(tv, o, A1, A2);
 #pragma unroll
         for (int s = 1; s < J; s <<= 1) {
 #pragma unroll

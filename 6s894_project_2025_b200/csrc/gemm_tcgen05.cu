@@ -276,6 +276,24 @@ int encode_tmap_bf16_2d(CUtensorMap *map, const void *base, uint64_t rows, uint6
     return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
+// 3-D view of a row-major bf16 matrix (rows x cols, cols % 64 == 0) as [64 k][rows][cols/64 chunks], so that
+// one box {64, box_rows, box_chunks} fetches box_rows x (64*box_chunks) elements and lands in shared memory as
+// box_chunks consecutive K-major tiles of box_rows x 128 bytes with 128-byte swizzle.
+int encode_tmap_bf16_rows_chunks(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols,
+                                 uint32_t box_rows, uint32_t box_chunks)
+{
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return (int)cudaErrorNotSupported;
+    const cuuint64_t dims[3] = {64, rows, cols / 64};
+    const cuuint64_t strides[2] = {cols * 2, 128};
+    const cuuint32_t box[3] = {64, box_rows, box_chunks};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
 static int sm_count_tc()
 {
     int dev = 0, n = 148;

@@ -82,6 +82,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
         "l"(map), "r"(x), "r"(y), "r"(bar)
         : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, int x, int y, int z, uint32_t bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n" ::"r"(dst),
+        "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+        : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *map)
 {
     asm volatile("prefetch.tensormap [%0];\n" ::"l"(map) : "memory");
@@ -156,5 +163,8 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // with a box of box_rows x 64 columns and 128-byte swizzle.  Returns 0 or a
 // CUresult (positive).
 int encode_tmap_bf16_2d(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows);
+// Host: 3-D view [64 k][rows][cols/64] of the same matrix; box = box_rows x (64*box_chunks) elements.
+int encode_tmap_bf16_rows_chunks(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols,
+                                 uint32_t box_rows, uint32_t box_chunks);
 
 }  // namespace b200ht
