@@ -371,14 +371,49 @@ def run_gpu_arm(args):
         dist.destroy_process_group()
 
 
+def run_profile_case(case: str):
+    """A handful of launches on a reduced shape (inputs larger than the 126 MB L2, a
+    few hundred MB on the device) so that an ncu capture of the kernel ends quickly."""
+    import torch
+
+    pkg = importlib.import_module("6s894_project_2025_b200")
+    torch.cuda.set_device(0)
+    g = torch.Generator(device="cuda").manual_seed(0)
+    if case == "gemm":      # fused W.H(X): K=8192, M=8192, 4096 tokens  (W 134 MB, X 67 MB, C 67 MB)
+        K, M, N = 8192, 8192, 4096
+        W = (torch.randn(M, K, generator=g, device="cuda") / math.sqrt(K)).bfloat16()
+        X = torch.randn(N, K, generator=g, device="cuda").bfloat16()
+        for _ in range(4):
+            C = pkg.fused_ht_gemm(X, W, out_layout="nm", out_dtype=torch.bfloat16)
+        print("gemm case done", float(C.float().abs().mean()))
+    elif case == "fwht":    # standalone transform, 4096 rows, n = 1024 and 32768 (bf16), distinct buffers
+        for n, rows in ((1024, 65536), (32768, 4096)):
+            bufs = [torch.randn(rows, n, generator=g, device="cuda").bfloat16() for _ in range(3)]
+            for b in bufs:
+                y = pkg.hadamard_transform(b)
+            print("fwht case", n, float(y.float().abs().mean()))
+    else:                   # fused GEMV, W 4096 x 4096 bf16, B = 16 and 1, distinct W buffers
+        Ws = [(torch.randn(4096, 4096, generator=g, device="cuda") / 64).bfloat16() for _ in range(6)]
+        for B in (16, 1):
+            X = torch.randn(4096, B, generator=g, device="cuda").bfloat16()
+            for W in Ws:
+                Y = pkg.fused_ht_gemv(W, X)
+            print("gemv case", B, float(Y.abs().mean()))
+    torch.cuda.synchronize()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--profile-case", default=None, choices=["gemm", "fwht", "gemv"],
+                    help="run a few launches of ONE kernel on a reduced shape and exit (for ncu captures)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.profile_case:
+        run_profile_case(args.profile_case)
+    elif args.impl == "reference":
         run_reference_arm(args)
     else:
         run_gpu_arm(args)
