@@ -23,7 +23,7 @@ ROOT = HERE.parent
 OUT = HERE / "libb200ht.so"
 OBJ_DIR = HERE / "build"
 
-SOURCES = ["api.cu", "fwht.cu", "fused_gemm.cu", "gemm_tcgen05.cu", "fused_gemv.cu"]
+SOURCES = ["api.cu", "fwht.cu", "fwht_tcgen05.cu", "fused_gemm.cu", "gemm_tcgen05.cu", "fused_gemv.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -31,6 +31,7 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC",
     "--expt-relaxed-constexpr",
     *(["-DB200HT_GEMV_TRACE"] if os.environ.get("B200HT_GEMV_TRACE") else []),  # developer timing hooks
+    *(["-DB200HT_FWHT_TRACE"] if os.environ.get("B200HT_FWHT_TRACE") else []),
     "-I", str(ROOT / "include"),
 ]
 

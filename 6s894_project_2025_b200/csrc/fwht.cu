@@ -8,14 +8,27 @@
 // below the memory time; data moves with 16-byte, fully coalesced accesses.
 //
 //   n = 8 .. 2048   fwht_reg_kernel : a warp keeps whole rows in registers
-//   n = 4096 .. 32768 fwht_smem_kernel: a CTA keeps a slab of rows in padded
+//   n = 4096 .. 16384 fwht_smem_kernel: a CTA keeps a slab of rows in padded
 //                     shared memory; low 8 index bits in pass 1, the rest in pass 2
+//   n = 32768       fwht_tc_kernel (fwht_tcgen05.cu): tcgen05 + TMEM; falls back to
+//                     fwht_smem_kernel for buffers that are not 128-byte aligned
 //   n = 2, 4        fwht_tiny_kernel : one thread per row
 //   fp32            fwht_f32_kernel  : exact fp32 butterflies in shared memory
 #include "common.cuh"
 #include "fwht_f32.cuh"
 
+#include <cstdlib>
+
 namespace b200ht {
+
+int launch_fwht_tc(const void *in, void *out, uint64_t rows, int logn, int dtype, float scale, cudaStream_t st);
+// Smallest log2(n) sent to the tcgen05 kernel; B200HT_FWHT_TC_MIN=<log2 n> overrides it (tuning knob).
+static int tc_min_logn()
+{
+    const char *e = std::getenv("B200HT_FWHT_TC_MIN");
+    if (e && e[0] >= '0' && e[0] <= '9') return std::atoi(e);
+    return 15;
+}
 
 // ---------------------------------------------------------------------------
 // n <= 2048, 16-bit: rows live in one warp's registers.
@@ -311,6 +324,15 @@ int launch_fwht(const void *in, void *out, uint64_t rows, uint32_t n, int dtype,
 {
     const int logn = ilog2(n);
     if (dtype == B200HT_F32) return launch_fwht_f32((const float *)in, (float *)out, rows, logn, scale, st);
+    // n = 32768: tcgen05 kernel (fwht_tcgen05.cu; needs 128-byte aligned pointers for TMA).  It is correct for
+    // every n >= 256; B200HT_FWHT_TC_MIN=<log2 n> lowers the threshold, B200HT_FWHT_MMA_SYNC=1 disables it.
+    static const int kTcMinLogN = tc_min_logn();
+    static const bool use_mma_sync = [] {
+        const char *e = std::getenv("B200HT_FWHT_MMA_SYNC");
+        return e && e[0] == '1';
+    }();
+    if (logn >= kTcMinLogN && !use_mma_sync && ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 127u) == 0)
+        return launch_fwht_tc(in, out, rows, logn, dtype, scale, st);
     if (dtype == B200HT_BF16) return launch_b16<B200HT_BF16>(in, out, rows, logn, scale, st);
     return launch_b16<B200HT_F16>(in, out, rows, logn, scale, st);
 }

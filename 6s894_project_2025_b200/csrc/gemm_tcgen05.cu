@@ -262,7 +262,8 @@ static EncodeTiledFn get_encode_fn()
     return fn;
 }
 
-int encode_tmap_bf16_2d(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows)
+int encode_tmap_b16_2d(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                       int dtype)
 {
     EncodeTiledFn fn = get_encode_fn();
     if (!fn) return (int)cudaErrorNotSupported;
@@ -270,10 +271,16 @@ int encode_tmap_bf16_2d(CUtensorMap *map, const void *base, uint64_t rows, uint6
     const cuuint64_t strides[1] = {cols * 2};
     const cuuint32_t box[2] = {64, box_rows};
     const cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const CUtensorMapDataType dt =
+        dtype == B200HT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUresult r = fn(map, dt, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+int encode_tmap_bf16_2d(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows)
+{
+    return encode_tmap_b16_2d(map, base, rows, cols, box_rows, B200HT_BF16);
 }
 
 // 3-D view of a row-major bf16 matrix (rows x cols, cols % 64 == 0) as [64 k][rows][cols/64 chunks], so that

@@ -163,6 +163,9 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // with a box of box_rows x 64 columns and 128-byte swizzle.  Returns 0 or a
 // CUresult (positive).
 int encode_tmap_bf16_2d(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows);
+// Same for fp16 or bf16 (dtype = B200HT_F16 | B200HT_BF16).
+int encode_tmap_b16_2d(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                       int dtype);
 // Host: 3-D view [64 k][rows][cols/64] of the same matrix; box = box_rows x (64*box_chunks) elements.
 int encode_tmap_bf16_rows_chunks(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols,
                                  uint32_t box_rows, uint32_t box_chunks);

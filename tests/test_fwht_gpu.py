@@ -135,3 +135,34 @@ def test_fp32_entry_is_exact_to_fp32(pkg, lib, oracle):
         assert rc == 0, lib.error_string(rc)
         ref = oracle.fwht_rows(x.double().numpy())
         assert oracle.rel_fro(out.cpu().numpy(), ref) <= 1e-6
+
+
+@pytest.mark.parametrize("logn", [8, 10, 12, 13, 14, 15])
+@pytest.mark.parametrize("dtype,atol", [(torch.float16, 1e-2), (torch.bfloat16, 5e-2)])
+def test_tcgen05_kernel_all_sizes(lib, oracle, logn, dtype, atol):
+    """The tcgen05/TMEM kernel is dispatched for n = 32768 only, but it is written for every
+    n >= 256: call it directly (B200HT_FWHT_TC_MIN is read at first use, so a child process
+    is used) and compare with the oracle, ragged row counts included."""
+    import os, subprocess, sys, textwrap
+    code = textwrap.dedent(f"""
+        import importlib, sys
+        sys.path.insert(0, {str(__import__('pathlib').Path(__file__).resolve().parent.parent)!r})
+        import numpy as np, torch
+        pkg = importlib.import_module("6s894_project_2025_b200")
+        oracle = importlib.import_module("oracle.fwht_oracle")
+        n = {1 << logn}
+        g = torch.Generator().manual_seed({logn})
+        for rows in (1, 3, 130, 517):
+            x = torch.randn(rows, n, generator=g).to({dtype})
+            y = pkg.hadamard_transform(x.cuda())
+            ref = oracle.fwht_rows(x.double().numpy())
+            err = float(np.max(np.abs(y.double().cpu().numpy() - ref)))
+            assert err <= {atol}, (rows, err)
+            xi = x.cuda(); pkg.hadamard_transform(xi, inplace=True)
+            assert torch.equal(xi, y)
+        assert pkg.device_status() == 0
+        print("ok")
+    """)
+    env = dict(os.environ, B200HT_FWHT_TC_MIN="8")
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=300)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stdout + r.stderr
