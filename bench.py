@@ -19,6 +19,7 @@ no collective on the data path), so total work is fixed: strong scaling.
   fwht      secondary block: standalone transform of (16384, n) bf16, n = 2^8..
             2^15, HBM GB/s against the measured copy bandwidth
   gemv      secondary block: fused GEMV, W 4096 x 4096 bf16, B = 1, 4, 16, GB/s
+  c3        secondary block: fused W.H(X) at K=1024, 4096 tokens, M=4096, fp32 and bf16
   cpu_baseline  the reference's torch path (explicit Hadamard matmul, then
             matmul; bench/bench.py:44-59 of the reference) on the host cores,
             on a bounded slice of the same tokens
@@ -72,7 +73,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -233,6 +234,35 @@ def time_gemv(pkg, torch, peaks, reps=20):
     return out
 
 
+def time_c3(pkg, torch, peaks, reps=10):
+    """Fused W.H(X) at K=1024, 4096 tokens, M=4096: fp32 (exact FFMA path) and bf16 (tcgen05 path)."""
+    K, N, M = 1024, 4096, 4096
+    g = torch.Generator(device="cuda").manual_seed(2)
+    out = {}
+    for name, dt in (("fp32", torch.float32), ("bf16", torch.bfloat16)):
+        # 4 rotating input sets (X, W): 2 x 16/8 MB each, C 64 MB fp32 -> every call misses L2 for C at least
+        sets = [(torch.randn(N, K, generator=g, device="cuda").to(dt), torch.randn(M, K, generator=g, device="cuda").to(dt))
+                for _ in range(4)]
+        C = torch.empty(M, N, dtype=torch.float32, device="cuda")
+        ws = torch.empty(pkg.fused_gemm_workspace_bytes(M, N, K, dt), dtype=torch.uint8, device="cuda")
+        for X, W in sets[:3]:
+            pkg.fused_ht_gemm(X, W, out=C, workspace=ws)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            for X, W in sets:
+                pkg.fused_ht_gemm(X, W, out=C, workspace=ws)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / (reps * len(sets))
+        tf = 2.0 * M * N * K / (ms * 1e-3) / 1e12
+        peak = 74.0 if name == "fp32" else peaks["bf16_tflops"]
+        out[name] = {"ms": ms, "tflops": tf, "peak_tflops": peak, "frac": tf / peak,
+                     "peak_source": "nominal fp32 FFMA 148*128*2*1.965e9" if name == "fp32" else "measured cuBLAS bf16 burst"}
+    return out
+
+
 def run_gpu_arm(args):
     import torch
     import torch.distributed as dist
@@ -318,6 +348,7 @@ def run_gpu_arm(args):
 
     fwht = time_fwht_sweep(pkg, torch, peaks)
     gemv = time_gemv(pkg, torch, peaks)
+    c3 = time_c3(pkg, torch, peaks)
     if world > 1:
         agg = torch.tensor([fwht[k]["gbs"] for k in sorted(fwht, key=int)], device="cuda")
         dist.all_reduce(agg, op=dist.ReduceOp.SUM)
@@ -360,6 +391,7 @@ def run_gpu_arm(args):
                               "peak_source": f"{peaks['source']} copy bandwidth"},
             "fwht": fwht,
             "gemv": gemv,
+            "c3": c3,
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": X.numel() * 2 * world, "d2h_bytes_per_step": C.numel() * 2 * world},
