@@ -8,8 +8,11 @@
 // below the memory time; data moves with 16-byte, fully coalesced accesses.
 //
 //   n = 8 .. 2048   fwht_reg_kernel : a warp keeps whole rows in registers
-//   n = 4096 .. 16384 fwht_smem_kernel: a CTA keeps a slab of rows in padded
-//                     shared memory; low 8 index bits in pass 1, the rest in pass 2
+//   n = 4096        fwht_smem2_kernel: a CTA keeps a slab of rows in shared memory;
+//                     index bits 0..9 in pass 1 (tensor cores + fp32), bits 10, 11 in
+//                     pass 2 (fp32 register butterflies)
+//   n = 8192, 16384 fwht_smem_kernel: padded shared memory; low 8 index bits in pass
+//                     1, the rest in pass 2, both through rot8
 //   n = 32768       fwht_tc_kernel (fwht_tcgen05.cu): tcgen05 + TMEM; falls back to
 //                     fwht_smem_kernel for buffers that are not 128-byte aligned
 //   n = 2, 4        fwht_tiny_kernel : one thread per row
@@ -89,7 +92,7 @@ __global__ void __launch_bounds__(256) fwht_reg_kernel(const uint4 *in, uint4 *o
 }
 
 // ---------------------------------------------------------------------------
-// n = 4096 .. 32768, 16-bit: a CTA of 8 warps holds a slab of SLAB_ROWS rows in
+// n = 8192, 16384 (and 32768 for unaligned buffers), 16-bit: a CTA of 8 warps holds a slab of SLAB_ROWS rows in
 // shared memory.  Chunk c (256 elements = 32 vectors) sits at vector offset 33*c
 // so that both the contiguous accesses of pass 1 and the chunk-strided accesses
 // of pass 2 are bank-conflict free.
@@ -202,6 +205,148 @@ __global__ void __launch_bounds__(256) fwht_smem_kernel(const uint4 *in, uint4 *
 }
 
 // ---------------------------------------------------------------------------
+// n = 4096 (written for 4096 .. 32768), 16-bit, second variant: a CTA of 8 warps
+// holds a 32 KB slab of rows in shared memory, chunk c (256 elements = 32 vectors)
+// at vector offset 32c.
+//   pass 1: a warp takes 4 consecutive chunks: index bits 0..7 through rot8 (the
+//           only tensor-core work: 4 mma.sync per 256 elements, as for n <= 2048),
+//           bits 8, 9 as fp32 butterflies across the 4 chunks, result rounded to
+//           16 bit into shared memory
+//   pass 2: index bits 10..LOGN-1 without tensor cores: a thread loads 4 vectors
+//           that differ in two of those bits (fp32 register butterflies), further
+//           bits sit on the high lane bits (shuffle butterflies); the low lane
+//           bits are consecutive vectors, so shared-memory reads are conflict free
+//           and the results go straight to global memory in segments of 64..512
+//           contiguous bytes.
+// The SM sustains about one mma.sync.m16n8k16 per 5.5 cycles, which the two-rot8
+// kernel above reaches at HBM speed; keeping the second pass off the tensor pipe
+// wins at n = 4096 (two register bits, no shuffles: 5.69 vs 5.41 TB/s) and loses
+// at n >= 8192, where the extra bits need shuffles (5.80 vs 6.06, 5.46 vs 5.94).
+// ---------------------------------------------------------------------------
+template <int LOGN>
+struct Smem2Cfg {
+    static constexpr int SLAB_ELEMS = LOGN >= 15 ? (1 << 15) : (1 << 14);
+    static constexpr int SLAB_ROWS = SLAB_ELEMS >> LOGN;
+    static constexpr int CPR = 1 << (LOGN - 8);             // chunks per row
+    static constexpr int NCHUNK = SLAB_ROWS * CPR;
+    static constexpr int SMEM_BYTES = NCHUNK * 32 * 16;
+    static constexpr int Q = LOGN - 10;                     // index bits left for pass 2
+    static constexpr int RB = Q < 2 ? Q : 2;                // ... in registers
+    static constexpr int SB = Q - RB;                       // ... on the high lane bits
+};
+
+template <int DT, int LOGN>
+__global__ void __launch_bounds__(256) fwht_smem2_kernel(const uint4 *in, uint4 *out, uint64_t rows,
+                                                         float mult)
+{
+    using Cfg = Smem2Cfg<LOGN>;
+    constexpr int CPR = Cfg::CPR, RB = Cfg::RB, SB = Cfg::SB, J = 1 << RB;
+    extern __shared__ uint4 sm[];
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const uint64_t row0 = (uint64_t)blockIdx.x * Cfg::SLAB_ROWS;
+    const int rows_here = (int)((rows - row0) < (uint64_t)Cfg::SLAB_ROWS ? (rows - row0)
+                                                                          : (uint64_t)Cfg::SLAB_ROWS);
+    const int chunks_here = rows_here * CPR;
+    const uint4 *gin = in + row0 * (uint64_t)(CPR * 32);
+    uint4 *gout = out + row0 * (uint64_t)(CPR * 32);
+
+    // ---- pass 1
+    {
+        uint32_t A1[4], A2[4];
+        make_hfrag<DT>(A1, lane, 15u, 0.25f);
+        make_hfrag<DT>(A2, lane, 15u, 0.25f);
+        for (int g0 = warp * 4; g0 < chunks_here; g0 += 8 * 4) {
+            uint4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = ld_stream(gin + (g0 + u) * 32 + lane);
+            float o[4][8];
+            rot8x<DT, 4>(v, o, A1, A2);
+#pragma unroll
+            for (int s = 1; s < 4; s <<= 1) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (!(u & s)) {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const float x = o[u][e], y = o[u | s][e];
+                            o[u][e] = x + y;
+                            o[u | s][e] = x - y;
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                uint4 r;
+                r.x = pack2<DT>(o[u][0], o[u][1]);
+                r.y = pack2<DT>(o[u][2], o[u][3]);
+                r.z = pack2<DT>(o[u][4], o[u][5]);
+                r.w = pack2<DT>(o[u][6], o[u][7]);
+                sm[(g0 + u) * 32 + lane] = r;
+            }
+        }
+    }
+    __syncthreads();
+
+    // ---- pass 2: chunk-index bits 2.. of the row (element bits 10..)
+    constexpr int SLOTS = 32 >> SB;                // consecutive vectors handled by the low lane bits
+    const int lane_lo = lane & (SLOTS - 1), lane_hi = lane >> (5 - SB);
+    const int ntasks = rows_here * 4 * (1 << SB);  // (row, chunk low 2 bits, slot block)
+    for (int task = warp; task < ntasks; task += 8) {
+        const int sblk = task & ((1 << SB) - 1);
+        const int clow = (task >> SB) & 3;
+        const int row = task >> (SB + 2);
+        const int slot = sblk * SLOTS + lane_lo;
+        const int chunk0 = row * CPR + clow + 4 * (J * lane_hi);   // + 4 * j
+        float f[J][8];
+#pragma unroll
+        for (int j = 0; j < J; ++j) {
+            const uint4 t = sm[(chunk0 + 4 * j) * 32 + slot];
+            const float2 a = unpack2<DT>(t.x), b = unpack2<DT>(t.y), c = unpack2<DT>(t.z), d = unpack2<DT>(t.w);
+            f[j][0] = a.x; f[j][1] = a.y; f[j][2] = b.x; f[j][3] = b.y;
+            f[j][4] = c.x; f[j][5] = c.y; f[j][6] = d.x; f[j][7] = d.y;
+        }
+#pragma unroll
+        for (int s = 1; s < J; s <<= 1) {
+#pragma unroll
+            for (int j = 0; j < J; ++j) {
+                if (!(j & s)) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const float x = f[j][e], y = f[j | s][e];
+                        f[j][e] = x + y;
+                        f[j | s][e] = x - y;
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int sb = 0; sb < SB; ++sb) {
+            const int m = 1 << (5 - SB + sb);
+            const bool upper = (lane & m) != 0;
+#pragma unroll
+            for (int j = 0; j < J; ++j) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float other = __shfl_xor_sync(0xffffffffu, f[j][e], m);
+                    f[j][e] = upper ? other - f[j][e] : f[j][e] + other;
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < J; ++j) {
+            uint4 r;
+            r.x = pack2<DT>(f[j][0] * mult, f[j][1] * mult);
+            r.y = pack2<DT>(f[j][2] * mult, f[j][3] * mult);
+            r.z = pack2<DT>(f[j][4] * mult, f[j][5] * mult);
+            r.w = pack2<DT>(f[j][6] * mult, f[j][7] * mult);
+            st_stream(gout + (chunk0 + 4 * j) * 32 + slot, r);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
 // n = 2, 4 (16-bit): one thread per row.
 // ---------------------------------------------------------------------------
 template <int DT>
@@ -276,6 +421,20 @@ static int launch_smem(const void *in, void *out, uint64_t rows, float scale, cu
     return (int)cudaGetLastError();
 }
 
+template <int DT, int LOGN>
+static int launch_smem2(const void *in, void *out, uint64_t rows, float scale, cudaStream_t st)
+{
+    using Cfg = Smem2Cfg<LOGN>;
+    const uint64_t blocks = (rows + Cfg::SLAB_ROWS - 1) / Cfg::SLAB_ROWS;
+    if (blocks > 0x7fffffffull) return B200HT_ERR_SIZE;
+    cudaError_t e = cudaFuncSetAttribute(fwht_smem2_kernel<DT, LOGN>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    fwht_smem2_kernel<DT, LOGN><<<(unsigned)blocks, 256, Cfg::SMEM_BYTES, st>>>(
+        (const uint4 *)in, (uint4 *)out, rows, scale * 16.0f);
+    return (int)cudaGetLastError();
+}
+
 template <int DT>
 static int launch_b16(const void *in, void *out, uint64_t rows, int logn, float scale, cudaStream_t st)
 {
@@ -297,7 +456,7 @@ static int launch_b16(const void *in, void *out, uint64_t rows, int logn, float 
     case 9: return launch_reg<DT, 9>(in, out, rows, scale, st);
     case 10: return launch_reg<DT, 10>(in, out, rows, scale, st);
     case 11: return launch_reg<DT, 11>(in, out, rows, scale, st);
-    case 12: return launch_smem<DT, 12>(in, out, rows, scale, st);
+    case 12: return launch_smem2<DT, 12>(in, out, rows, scale, st);
     case 13: return launch_smem<DT, 13>(in, out, rows, scale, st);
     case 14: return launch_smem<DT, 14>(in, out, rows, scale, st);
     case 15: return launch_smem<DT, 15>(in, out, rows, scale, st);

@@ -13,17 +13,28 @@
 //               store, while the next tile accumulates in the other TMEM half
 // Every mbarrier wait is time-limited; on expiry the CTA drains and exits and
 // the device status word carries B200HT_ERR_TIMEOUT.
+#include <cstdlib>
 #include <mutex>
 
 #include "tc_common.cuh"
 
 namespace b200ht {
 
-constexpr int TC_BM = 128, TC_BN = 256, TC_BK = 64, TC_STAGES = 4;
-constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;  // 16 KB
-constexpr int TC_B_BYTES = TC_BN * TC_BK * 2;  // 32 KB
-constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
-constexpr int TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+// CTA tile: (128 * MT) rows of W x 256 tokens x 64 k per stage.  MT = 2 halves the operand bytes fetched per flop
+// (the token tile is shared by two 128-row MMAs) at the price of a single accumulator set, i.e. an epilogue that
+// is not overlapped with the next tile; MT = 1 double-buffers the accumulator and gives twice as many tiles.
+constexpr int TC_BN = 256, TC_BK = 64;
+template <int MT>
+struct TcCfg {
+    static constexpr int BM = 128 * MT;
+    static constexpr int STAGES = MT == 1 ? 4 : 3;
+    static constexpr int A_BYTES = BM * TC_BK * 2;      // 16 / 32 KB
+    static constexpr int B_BYTES = TC_BN * TC_BK * 2;   // 32 KB
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+    static constexpr int NACC = MT == 1 ? 2 : 1;        // accumulator sets in TMEM
+    static constexpr int THREADS = 64 + 128 * MT;       // TMA warp, MMA warp, 4 * MT epilogue warps
+};
 
 template <int OUT_DT, int LAYOUT>
 __device__ __forceinline__ void tc_store_chunk(void *C, int M, int N, int m, int n, const uint32_t (&r)[32])
@@ -86,33 +97,35 @@ __device__ __forceinline__ void tc_tile_coord(int tile, int mt, int nt, int &mb,
     mb = grp * TC_GROUP_M + (rem - nb * gsz);
 }
 
-template <int OUT_DT, int LAYOUT>
-__global__ void __launch_bounds__(192, 1)
+template <int OUT_DT, int LAYOUT, int MT>
+__global__ void __launch_bounds__(TcCfg<MT>::THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmY, void *C, int M,
                int N, int K, int *status)
 {
+    using Cfg = TcCfg<MT>;
+    constexpr int STAGES = Cfg::STAGES, STAGE_BYTES = Cfg::STAGE_BYTES, NACC = Cfg::NACC;
     extern __shared__ unsigned char smem_dyn[];
     const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
-    const uint32_t bar_base = base + TC_STAGES * TC_STAGE_BYTES;
+    const uint32_t bar_base = base + STAGES * STAGE_BYTES;
     // barriers: full[S], empty[S], tmem_full[2], tmem_empty[2]; then tmem address slot, abort flag
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
-    auto empty_bar = [&](int s) { return bar_base + 8u * (TC_STAGES + s); };
-    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * TC_STAGES + a); };
-    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * TC_STAGES + 2 + a); };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
     unsigned char *gen_base = smem_dyn + (base - smem_u32(smem_dyn));
-    uint32_t *tmem_slot = (uint32_t *)(gen_base + TC_STAGES * TC_STAGE_BYTES + 8 * (2 * TC_STAGES + 4));
+    uint32_t *tmem_slot = (uint32_t *)(gen_base + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 4));
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < TC_STAGES; ++s) {
+        for (int s = 0; s < STAGES; ++s) {
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tfull_bar(a), 1);
-            mbar_init(tempty_bar(a), 4);  // one arrival per epilogue warp
+            mbar_init(tempty_bar(a), 4 * MT);  // one arrival per epilogue warp
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -125,7 +138,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int mt = (M + TC_BM - 1) / TC_BM, nt = (N + TC_BN - 1) / TC_BN;
+    const int mt = (M + Cfg::BM - 1) / Cfg::BM, nt = (N + TC_BN - 1) / TC_BN;
     const int ntiles = mt * nt;
     const int kblocks = K / TC_BK;
 
@@ -136,24 +149,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
                 int mb, nb;
                 tc_tile_coord(tile, mt, nt, mb, nb);
-                const int m0 = mb * TC_BM, n0 = nb * TC_BN;
+                const int m0 = mb * Cfg::BM, n0 = nb * TC_BN;
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                    const int s = it % TC_STAGES;
-                    const uint32_t ph = (it / TC_STAGES) & 1u;
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1u;
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, status)) { ok = false; break; }
-                    mbar_expect_tx(full_bar(s), TC_STAGE_BYTES);
-                    const uint32_t sa = base + s * TC_STAGE_BYTES;
+                    mbar_expect_tx(full_bar(s), STAGE_BYTES);
+                    const uint32_t sa = base + s * STAGE_BYTES;
                     tma_load_2d(sa, &tmW, kb * TC_BK, m0, full_bar(s));
-                    tma_load_2d(sa + TC_A_BYTES, &tmY, kb * TC_BK, n0, full_bar(s));
+                    tma_load_2d(sa + Cfg::A_BYTES, &tmY, kb * TC_BK, n0, full_bar(s));
                 }
             }
             if (!ok) {
                 // copies already issued still land in this CTA's shared memory: give them time
-                const uint32_t pending = it < (uint32_t)TC_STAGES ? it : (uint32_t)TC_STAGES;
+                const uint32_t pending = it < (uint32_t)STAGES ? it : (uint32_t)STAGES;
                 for (uint32_t j = 0; j < pending; ++j) {
                     const uint32_t i2 = it - 1 - j;
                     const uint64_t t0 = global_ns();
-                    while (!mbar_test(full_bar(i2 % TC_STAGES), (i2 / TC_STAGES) & 1u) &&
+                    while (!mbar_test(full_bar(i2 % STAGES), (i2 / STAGES) & 1u) &&
                            global_ns() - t0 < 100000000ull) {}
                 }
             }
@@ -161,26 +174,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         __syncwarp();
     } else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc_bf16(TC_BM, TC_BN);
+            constexpr uint32_t idesc = umma_idesc_bf16(128, TC_BN);
             uint32_t it = 0, tcount = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tcount) {
-                const int acc = tcount & 1;
-                const uint32_t aph = (tcount >> 1) & 1u;
+                const int acc = tcount % NACC;
+                const uint32_t aph = (tcount / NACC) & 1u;
                 if (!mbar_wait(tempty_bar(acc), aph ^ 1u, abort_flag, status)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + acc * TC_BN;
+                const uint32_t d_tmem = tmem_base + acc * TC_BN;   // MT == 2: halves at columns 0 and 256
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                    const int s = it % TC_STAGES;
-                    const uint32_t ph = (it / TC_STAGES) & 1u;
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1u;
                     if (!mbar_wait(full_bar(s), ph, abort_flag, status)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t sa = base + s * TC_STAGE_BYTES;
-                    const uint64_t adesc = umma_desc_k_sw128(sa);
-                    const uint64_t bdesc = umma_desc_k_sw128(sa + TC_A_BYTES);
+                    const uint32_t sa = base + s * STAGE_BYTES;
+                    const uint64_t bdesc = umma_desc_k_sw128(sa + Cfg::A_BYTES);
 #pragma unroll
-                    for (int k = 0; k < TC_BK / 16; ++k)
-                        umma_bf16_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) ? 1u : 0u);
+                    for (int h = 0; h < MT; ++h) {
+                        const uint64_t adesc = umma_desc_k_sw128(sa + h * 16384);
+#pragma unroll
+                        for (int k = 0; k < TC_BK / 16; ++k)
+                            umma_bf16_ss(d_tmem + h * TC_BN, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) ? 1u : 0u);
+                    }
                     umma_commit(empty_bar(s));
                 }
                 if (ok) umma_commit(tfull_bar(acc));
@@ -188,19 +204,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         }
         __syncwarp();
     } else {
-        const int q = warp & 3;  // TMEM lane quadrant this warp may read
+        const int q = warp & 3;          // TMEM lane quadrant this warp may read
+        const int h = (warp - 2) >> 2;   // 128-row half of the tile drained by this warp
         uint32_t tcount = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tcount) {
-            const int acc = tcount & 1;
-            const uint32_t aph = (tcount >> 1) & 1u;
+            const int acc = tcount % NACC;
+            const uint32_t aph = (tcount / NACC) & 1u;
             int mb, nb;
             tc_tile_coord(tile, mt, nt, mb, nb);
-            const int m0 = mb * TC_BM, n0 = nb * TC_BN;
+            const int m0 = mb * Cfg::BM, n0 = nb * TC_BN;
             if (!mbar_wait(tfull_bar(acc), aph, abort_flag, status)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * TC_BN;
-            const int m = m0 + q * 32 + lane;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (acc + h) * TC_BN;
+            const int m = m0 + h * 128 + q * 32 + lane;
 #pragma unroll 1
             for (int c = 0; c < TC_BN; c += 32) {
                 uint32_t r[32];
@@ -308,16 +325,36 @@ static int sm_count_tc()
     return n;
 }
 
-template <int OUT_DT, int LAYOUT>
-static int launch_tc(const CUtensorMap &tw, const CUtensorMap &ty, void *C, int M, int N, int K, cudaStream_t st)
+template <int OUT_DT, int LAYOUT, int MT>
+static int launch_tc_mt(const void *Y, const void *W, void *C, int M, int N, int K, cudaStream_t st)
 {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<OUT_DT, LAYOUT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         TC_SMEM_BYTES);
+    using Cfg = TcCfg<MT>;
+    CUtensorMap tw, ty;
+    int rc = encode_tmap_bf16_2d(&tw, W, (uint64_t)M, (uint64_t)K, Cfg::BM);
+    if (rc) return rc;
+    rc = encode_tmap_bf16_2d(&ty, Y, (uint64_t)N, (uint64_t)K, TC_BN);
+    if (rc) return rc;
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<OUT_DT, LAYOUT, MT>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
-    const int tiles = ((M + TC_BM - 1) / TC_BM) * ((N + TC_BN - 1) / TC_BN);
+    const int tiles = ((M + Cfg::BM - 1) / Cfg::BM) * ((N + TC_BN - 1) / TC_BN);
     const int grid = tiles < sm_count_tc() ? tiles : sm_count_tc();
-    gemm_tc_kernel<OUT_DT, LAYOUT><<<grid, 192, TC_SMEM_BYTES, st>>>(tw, ty, C, M, N, K, status_word_ptr());
+    gemm_tc_kernel<OUT_DT, LAYOUT, MT><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(tw, ty, C, M, N, K,
+                                                                                    status_word_ptr());
     return (int)cudaGetLastError();
+}
+
+template <int OUT_DT, int LAYOUT>
+static int launch_tc(const void *Y, const void *W, void *C, int M, int N, int K, cudaStream_t st)
+{
+    // 256-row tiles when there are at least four waves of them, else 128-row tiles
+    static const int force_mt = [] {
+        const char *e = std::getenv("B200HT_GEMM_MT");
+        return e ? std::atoi(e) : 0;
+    }();
+    const long tiles256 = (long)((M + 255) / 256) * ((N + TC_BN - 1) / TC_BN);
+    const bool big = force_mt ? force_mt == 2 : tiles256 >= 4L * sm_count_tc();
+    return big ? launch_tc_mt<OUT_DT, LAYOUT, 2>(Y, W, C, M, N, K, st) : launch_tc_mt<OUT_DT, LAYOUT, 1>(Y, W, C, M, N, K, st);
 }
 
 int launch_gemm_bf16_tcgen05(const void *Y, const void *W, void *C, int M, int N, int K, int out_dtype,
@@ -329,17 +366,12 @@ int launch_gemm_bf16_tcgen05(const void *Y, const void *W, void *C, int M, int N
                                                      out_dtype, out_layout);
         return (int)cudaGetLastError();
     }
-    CUtensorMap tw, ty;
-    int rc = encode_tmap_bf16_2d(&tw, W, (uint64_t)M, (uint64_t)K, TC_BM);
-    if (rc) return rc;
-    rc = encode_tmap_bf16_2d(&ty, Y, (uint64_t)N, (uint64_t)K, TC_BN);
-    if (rc) return rc;
     if (out_dtype == B200HT_F32) {
-        return out_layout == B200HT_OUT_MN ? launch_tc<B200HT_F32, B200HT_OUT_MN>(tw, ty, C, M, N, K, st)
-                                           : launch_tc<B200HT_F32, B200HT_OUT_NM>(tw, ty, C, M, N, K, st);
+        return out_layout == B200HT_OUT_MN ? launch_tc<B200HT_F32, B200HT_OUT_MN>(Y, W, C, M, N, K, st)
+                                           : launch_tc<B200HT_F32, B200HT_OUT_NM>(Y, W, C, M, N, K, st);
     }
-    return out_layout == B200HT_OUT_MN ? launch_tc<B200HT_BF16, B200HT_OUT_MN>(tw, ty, C, M, N, K, st)
-                                       : launch_tc<B200HT_BF16, B200HT_OUT_NM>(tw, ty, C, M, N, K, st);
+    return out_layout == B200HT_OUT_MN ? launch_tc<B200HT_BF16, B200HT_OUT_MN>(Y, W, C, M, N, K, st)
+                                       : launch_tc<B200HT_BF16, B200HT_OUT_NM>(Y, W, C, M, N, K, st);
 }
 
 }  // namespace b200ht
