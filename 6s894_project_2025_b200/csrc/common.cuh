@@ -35,6 +35,31 @@ int *status_word_ptr();  // device address of the status word on the current dev
 // Checks (once per device) that the current device is compute capability 10.x.
 int check_device();
 
+// Launch with programmatic stream serialization (programmatic dependent launch): the
+// kernel may be scheduled while its predecessor in the stream is still draining.  Every
+// kernel launched this way executes pdl_wait() before it touches global memory, which
+// blocks until all earlier work of the stream has completed and is visible, and
+// pdl_launch_dependents() as early as it likes.
+template <typename... KArgs, typename... Args>
+inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+#endif
+
 // ---------------------------------------------------------------------------
 // 16-bit packing
 // ---------------------------------------------------------------------------

@@ -285,6 +285,9 @@ gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bflo
         tma_prefetch_desc(&tmW);
     }
     __syncthreads();
+    // programmatic dependent launch: barrier set-up above overlaps the predecessor's tail
+    pdl_launch_dependents();
+    pdl_wait();
 
     // one TMA op per ring item: group_rows x (64*kc) elements of W
     auto issue = [&](int item) {
@@ -544,10 +547,9 @@ static int launch_stream_nt(const void *W, const void *X, void *Y, int M, int N,
     cudaError_t e =
         cudaFuncSetAttribute(gemv_bf16_stream_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    gemv_bf16_stream_kernel<NT><<<grid, GV_THREADS, smem, st>>>(tw, (const __nv_bfloat16 *)X, Y, M, N, logn, B, b0, Bg,
-                                                                out_dtype, scale, rows_per_cta, group_rows, kc,
-                                                                stage_bytes, stages, status_word_ptr());
-    return (int)cudaGetLastError();
+    return launch_pdl(gemv_bf16_stream_kernel<NT>, dim3(grid), dim3(GV_THREADS), smem, st, tw,
+                      (const __nv_bfloat16 *)X, Y, M, N, logn, B, b0, Bg, out_dtype, scale, rows_per_cta, group_rows, kc,
+                      stage_bytes, stages, status_word_ptr());
 }
 
 static int launch_stream(const void *W, const void *X, void *Y, int M, int N, int logn, int B, int b0, int Bg,

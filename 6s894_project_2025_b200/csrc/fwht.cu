@@ -44,6 +44,10 @@ __global__ void __launch_bounds__(256) fwht_reg_kernel(const uint4 *in, uint4 *o
     constexpr int P = LOGN < 8 ? LOGN : 8;
     constexpr int CPR = LOGN > 8 ? (1 << (LOGN - 8)) : 1;  // chunks per row
     constexpr int GRP = CPR > 4 ? CPR : 4;
+    // Programmatic dependent launch: let the next kernel of the stream be scheduled while this one
+    // drains, and wait here until everything before this kernel has completed and is visible.
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const uint64_t warp = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const uint64_t first = warp * (uint64_t)(GRP * 32);
@@ -117,6 +121,8 @@ __global__ void __launch_bounds__(256) fwht_smem_kernel(const uint4 *in, uint4 *
     using Cfg = SmemCfg<LOGN>;
     constexpr int Q = Cfg::Q, CPR = Cfg::CPR;
     extern __shared__ uint4 sm[];
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const uint64_t row0 = (uint64_t)blockIdx.x * Cfg::SLAB_ROWS;
@@ -242,6 +248,8 @@ __global__ void __launch_bounds__(256) fwht_smem2_kernel(const uint4 *in, uint4 
     using Cfg = Smem2Cfg<LOGN>;
     constexpr int CPR = Cfg::CPR, RB = Cfg::RB, SB = Cfg::SB, J = 1 << RB;
     extern __shared__ uint4 sm[];
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const uint64_t row0 = (uint64_t)blockIdx.x * Cfg::SLAB_ROWS;
@@ -402,9 +410,10 @@ static int launch_reg(const void *in, void *out, uint64_t rows, float scale, cud
     const uint64_t blocks = (warps + 7) / 8;
     if (blocks > 0x7fffffffull) return B200HT_ERR_SIZE;
     const float f = hfrag_c(popc4(rot8_mask1(P))) * hfrag_c(popc4(rot8_mask2(P)));
-    fwht_reg_kernel<DT, LOGN><<<(unsigned)blocks, 256, 0, st>>>((const uint4 *)in, (uint4 *)out,
-                                                                 total_vec, scale / f);
-    return (int)cudaGetLastError();
+    // programmatic dependent launch: the small sizes are bound by launch latency, and this lets the scheduling
+    // of back-to-back launches overlap (the kernel itself waits for its predecessors before touching memory)
+    return launch_pdl(fwht_reg_kernel<DT, LOGN>, dim3((unsigned)blocks), dim3(256), 0, st, (const uint4 *)in,
+                      (uint4 *)out, total_vec, scale / f);
 }
 
 template <int DT, int LOGN>
@@ -416,9 +425,8 @@ static int launch_smem(const void *in, void *out, uint64_t rows, float scale, cu
     cudaError_t e = cudaFuncSetAttribute(fwht_smem_kernel<DT, LOGN>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
-    fwht_smem_kernel<DT, LOGN><<<(unsigned)blocks, 256, Cfg::SMEM_BYTES, st>>>(
-        (const uint4 *)in, (uint4 *)out, rows, scale * 64.0f);
-    return (int)cudaGetLastError();
+    return launch_pdl(fwht_smem_kernel<DT, LOGN>, dim3((unsigned)blocks), dim3(256), (size_t)Cfg::SMEM_BYTES, st,
+                      (const uint4 *)in, (uint4 *)out, rows, scale * 64.0f);
 }
 
 template <int DT, int LOGN>
@@ -430,9 +438,8 @@ static int launch_smem2(const void *in, void *out, uint64_t rows, float scale, c
     cudaError_t e = cudaFuncSetAttribute(fwht_smem2_kernel<DT, LOGN>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
-    fwht_smem2_kernel<DT, LOGN><<<(unsigned)blocks, 256, Cfg::SMEM_BYTES, st>>>(
-        (const uint4 *)in, (uint4 *)out, rows, scale * 16.0f);
-    return (int)cudaGetLastError();
+    return launch_pdl(fwht_smem2_kernel<DT, LOGN>, dim3((unsigned)blocks), dim3(256), (size_t)Cfg::SMEM_BYTES, st,
+                      (const uint4 *)in, (uint4 *)out, rows, scale * 16.0f);
 }
 
 template <int DT>

@@ -228,6 +228,10 @@ fwht_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
     __syncthreads();
     tc_fence_after();
 
+    // the set-up above touched no global memory; from here on the predecessors' results are needed
+    pdl_launch_dependents();
+    pdl_wait();
+
     // work: pairs of consecutive tiles; iteration i of this CTA handles tile (i & 1) of pair blockIdx.x + (i >> 1) * grid
     const int npairs = (ntiles + 1) >> 1;
     const int my_pairs = npairs > (int)blockIdx.x ? (npairs - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
@@ -473,8 +477,8 @@ static int launch_ft(const void *in, void *out, uint64_t chunk_rows, int logn, f
     const int cpr_log = logn - 7;
     const int hbits = cpr_log > 7 ? 7 : cpr_log;
     const float applied = 0.125f * exp2f(-(float)(hbits / 2));
-    fwht_tc_kernel<DT><<<grid, FT_THREADS, FT_SMEM_BYTES, st>>>(tin, tout, ntiles, logn, scale / applied, status_word_ptr());
-    return (int)cudaGetLastError();
+    return launch_pdl(fwht_tc_kernel<DT>, dim3(grid), dim3(FT_THREADS), (size_t)FT_SMEM_BYTES, st, tin, tout, ntiles,
+                      logn, scale / applied, status_word_ptr());
 }
 
 // rows x n 16-bit, 128 <= n <= 32768, in/out 128-byte aligned (TMA); returns B200HT_ERR_ALIGN otherwise.
