@@ -347,13 +347,18 @@ static int launch_tc_mt(const void *Y, const void *W, void *C, int M, int N, int
 template <int OUT_DT, int LAYOUT>
 static int launch_tc(const void *Y, const void *W, void *C, int M, int N, int K, cudaStream_t st)
 {
-    // 256-row tiles when there are at least four waves of them, else 128-row tiles
+    // 256-row or 128-row CTA tiles: whichever needs less time in units of a 128-row tile, counting whole waves
+    // over the SMs (a 256-row tile costs two units; 128-row tiles pay about 3 % more for operand traffic).
+    // B200HT_GEMM_MT=1|2 forces one of them (tuning knob).
     static const int force_mt = [] {
         const char *e = std::getenv("B200HT_GEMM_MT");
         return e ? std::atoi(e) : 0;
     }();
-    const long tiles256 = (long)((M + 255) / 256) * ((N + TC_BN - 1) / TC_BN);
-    const bool big = force_mt ? force_mt == 2 : tiles256 >= 4L * sm_count_tc();
+    const long sms = sm_count_tc();
+    const long nt = (N + TC_BN - 1) / TC_BN;
+    const long tiles128 = (long)((M + 127) / 128) * nt, tiles256 = (long)((M + 255) / 256) * nt;
+    const double cost128 = 1.03 * (double)((tiles128 + sms - 1) / sms), cost256 = 2.0 * (double)((tiles256 + sms - 1) / sms);
+    const bool big = force_mt ? force_mt == 2 : (tiles256 >= sms && cost256 <= cost128);
     return big ? launch_tc_mt<OUT_DT, LAYOUT, 2>(Y, W, C, M, N, K, st) : launch_tc_mt<OUT_DT, LAYOUT, 1>(Y, W, C, M, N, K, st);
 }
 

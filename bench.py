@@ -383,7 +383,10 @@ def run_gpu_arm(args):
                        "l2": "inputs (W 470 MB + tokens) exceed the 126 MB L2; fwht sweep rotates >= 512 MB of buffers",
                        "out": "bf16 token-major"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": achieved / peak, "traffic": None,
+                         "frac": achieved / peak,
+                         # DRAM bytes of one full-size GEMM launch on one GPU, from the committed ncu capture
+                         # (profiles/gemm_tc_kernel_fused_k8192.md); scaled by the token share of a rank
+                         "traffic": 6.906e9 * n_local / N_TOKENS, "traffic_unit": "B/launch",
                          "peak_source": f"{peaks['source']} sustained cuBLAS bf16 (burst {peaks['bf16_tflops']})",
                          "frac_of_burst": achieved / peaks["bf16_tflops"]},
             "roofline_fwht": {"bound": "hbm", "achieved": best_fwht["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -411,15 +414,17 @@ def run_profile_case(case: str):
     pkg = importlib.import_module("6s894_project_2025_b200")
     torch.cuda.set_device(0)
     g = torch.Generator(device="cuda").manual_seed(0)
-    if case == "gemm":      # fused W.H(X): K=8192, M=8192, 4096 tokens  (W 134 MB, X 67 MB, C 67 MB)
-        K, M, N = 8192, 8192, 4096
+    if case in ("gemm", "gemm-full"):
+        # reduced: K=8192, M=8192, 4096 tokens (W 134 MB, X 67 MB, C 67 MB); full: the bench shape (1.95 GB on the
+        # device), meant for a one-pass capture of DRAM bytes only
+        K, M, N = (8192, 8192, 4096) if case == "gemm" else (K_DIM, M_DIM, N_TOKENS)
         W = (torch.randn(M, K, generator=g, device="cuda") / math.sqrt(K)).bfloat16()
         X = torch.randn(N, K, generator=g, device="cuda").bfloat16()
         for _ in range(4):
             C = pkg.fused_ht_gemm(X, W, out_layout="nm", out_dtype=torch.bfloat16)
         print("gemm case done", float(C.float().abs().mean()))
-    elif case == "fwht":    # standalone transform, 4096 rows, n = 1024 and 32768 (bf16), distinct buffers
-        for n, rows in ((1024, 65536), (32768, 4096)):
+    elif case == "fwht":    # standalone transform, n = 1024, 4096, 8192 and 32768 (bf16), 134-268 MB, distinct buffers
+        for n, rows in ((1024, 65536), (4096, 16384), (8192, 16384), (32768, 4096)):
             bufs = [torch.randn(rows, n, generator=g, device="cuda").bfloat16() for _ in range(3)]
             for b in bufs:
                 y = pkg.hadamard_transform(b)
@@ -440,7 +445,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--profile-case", default=None, choices=["gemm", "fwht", "gemv"],
+    ap.add_argument("--profile-case", default=None, choices=["gemm", "gemm-full", "fwht", "gemv"],
                     help="run a few launches of ONE kernel on a reduced shape and exit (for ncu captures)")
     args = ap.parse_args()
     if args.profile_case:
