@@ -4,6 +4,7 @@ The directory name starts with a digit, so import it with
 ``importlib.import_module("6s894_project_2025_b200")``.
 """
 from .ops import (  # noqa: F401
+    HostPipeline,
     device_status,
     fused_gemm_workspace_bytes,
     fused_ht_gemm,
@@ -13,6 +14,7 @@ from .ops import (  # noqa: F401
 from .partition import gather_result, shard_tokens, token_range  # noqa: F401
 
 __all__ = [
+    "HostPipeline",
     "hadamard_transform",
     "fused_ht_gemm",
     "fused_ht_gemv",

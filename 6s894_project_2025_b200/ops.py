@@ -128,6 +128,56 @@ def fused_ht_gemm(X: torch.Tensor, W: torch.Tensor, *, scale: float | None = Non
     return out
 
 
+class HostPipeline:
+    """Host-to-host fused W . H(X) for token batches that live in (pinned) host memory.
+
+    The tokens are cut into chunks; chunk i is copied in, multiplied and copied
+    out on stream i % n_streams, so the copy engines (one per direction) and the
+    SMs work on different chunks at the same time.  Device buffers are allocated
+    once.  The reference has no counterpart (its programs copy everything in,
+    run, copy everything out: fused_ht/fusion_pipelined.cu:626-704).
+    """
+
+    def __init__(self, W: torch.Tensor, max_tokens: int, *, chunk_tokens: int = 2048, n_streams: int = 3,
+                 out_dtype: torch.dtype = torch.bfloat16, scale: float | None = None):
+        if not W.is_cuda or W.dtype not in (torch.float32, torch.bfloat16):
+            raise RuntimeError("HostPipeline: W must be a float32 or bfloat16 CUDA tensor")
+        self.W = W.contiguous()
+        self.M, self.K = int(W.shape[0]), int(W.shape[1])
+        self.chunk = int(min(chunk_tokens, max(max_tokens, 1)))
+        self.out_dtype = out_dtype
+        self.scale = scale
+        dev = W.device
+        self.streams = [torch.cuda.Stream(device=dev) for _ in range(n_streams)]
+        self.x = [torch.empty(self.chunk, self.K, dtype=W.dtype, device=dev) for _ in range(n_streams)]
+        self.c = [torch.empty(self.chunk, self.M, dtype=out_dtype, device=dev) for _ in range(n_streams)]
+        nbytes = fused_gemm_workspace_bytes(self.M, self.chunk, self.K, W.dtype)
+        self.ws = [torch.empty(max(nbytes, 256), dtype=torch.uint8, device=dev) for _ in range(n_streams)]
+
+    def __call__(self, X_host: torch.Tensor, out_host: torch.Tensor) -> torch.Tensor:
+        """``out_host[t, m] = (W . H(x_t))[m]`` (token-major).  Both tensors should be pinned; returns
+        ``out_host`` after all chunks have been enqueued (synchronise before reading it)."""
+        n = int(X_host.shape[0])
+        if tuple(out_host.shape) != (n, self.M) or out_host.dtype != self.out_dtype:
+            raise RuntimeError("HostPipeline: out_host has the wrong shape or dtype")
+        cur = torch.cuda.current_stream(self.W.device)
+        for st in self.streams:
+            st.wait_stream(cur)
+        for i, t0 in enumerate(range(0, n, self.chunk)):
+            t1 = min(t0 + self.chunk, n)
+            k = i % len(self.streams)
+            with torch.cuda.stream(self.streams[k]):
+                xd = self.x[k][: t1 - t0]
+                cd = self.c[k][: t1 - t0]
+                xd.copy_(X_host[t0:t1], non_blocking=True)
+                fused_ht_gemm(xd, self.W, scale=self.scale, out_dtype=self.out_dtype, out_layout="nm", out=cd,
+                              workspace=self.ws[k])
+                out_host[t0:t1].copy_(cd, non_blocking=True)
+        for st in self.streams:
+            cur.wait_stream(st)
+        return out_host
+
+
 def fused_ht_gemv(W: torch.Tensor, X: torch.Tensor, *, scale: float | None = None,
                   out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
     """Y = W . H(X) for a small batch: ``Y[m, b] = sum_k W[m, k] * (scale * H_N x_b)[k]``.

@@ -154,3 +154,19 @@ def test_c5_full_size_sampled(pkg, oracle):
     ref_sum = Y @ W.double().numpy().sum(axis=0)
     got_sum = C[toks].double().sum(dim=1).cpu().numpy()
     assert oracle.rel_fro(got_sum, ref_sum) <= BF16_TOL
+
+
+def test_host_pipeline_matches_single_call(pkg, oracle):
+    inp = oracle.make_inputs("c5", K=1024, M=384, N=1000)
+    X, W = inp["X"], inp["W"]
+    Wd = W.cuda()
+    ref = pkg.fused_ht_gemm(X.cuda(), Wd, out_layout="nm", out_dtype=torch.bfloat16).cpu()
+    pipe = pkg.HostPipeline(Wd, 1000, chunk_tokens=256, n_streams=3)
+    Xh = X.pin_memory()
+    out = torch.empty(1000, 384, dtype=torch.bfloat16).pin_memory()
+    for _ in range(2):
+        out.zero_()
+        pipe(Xh, out)
+        torch.cuda.synchronize()
+        assert torch.equal(out, ref)
+    assert pkg.device_status() == 0
