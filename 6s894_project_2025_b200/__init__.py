@@ -12,6 +12,7 @@ from .ops import (  # noqa: F401
     hadamard_transform,
 )
 from .partition import gather_result, shard_tokens, token_range  # noqa: F401
+from . import torchlib  # noqa: F401  (registers torch.ops.b200ht.*)
 
 __all__ = [
     "HostPipeline",

@@ -1,0 +1,60 @@
+"""torch.library registration: dispatcher ops, fake-tensor shapes (CPU), and on the GPU opcheck, autograd of
+the transform and CUDA-graph capture/replay of all three operators."""
+import math
+
+import pytest
+import torch
+
+
+def test_ops_are_registered_with_fake_impls(pkg):
+    assert hasattr(torch.ops.b200ht, "hadamard_transform")
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    with FakeTensorMode():
+        x = torch.empty(3, 5, 256, dtype=torch.bfloat16, device="cuda")
+        y = torch.ops.b200ht.hadamard_transform(x, 1.0 / 16)
+        assert y.shape == x.shape and y.dtype == x.dtype
+        X = torch.empty(100, 1024, dtype=torch.bfloat16, device="cuda")
+        W = torch.empty(64, 1024, dtype=torch.bfloat16, device="cuda")
+        assert torch.ops.b200ht.fused_ht_gemm(X, W, 1.0, True, True).shape == (100, 64)
+        assert torch.ops.b200ht.fused_ht_gemm(X, W, 1.0, False, False).shape == (64, 100)
+        assert torch.ops.b200ht.fused_ht_gemm(X, W, 1.0, False, False).dtype == torch.float32
+        Xc = torch.empty(1024, 4, dtype=torch.bfloat16, device="cuda")
+        assert torch.ops.b200ht.fused_ht_gemv(W, Xc, 1.0, False).shape == (64, 4)
+
+
+@pytest.mark.gpu
+def test_opcheck_and_autograd(pkg, oracle):
+    x = torch.randn(4, 512, device="cuda").bfloat16()
+    torch.library.opcheck(torch.ops.b200ht.hadamard_transform, (x, 512 ** -0.5),
+                          test_utils=("test_schema", "test_faketensor"))
+    # H is symmetric and (with scale 1/sqrt(n)) orthogonal: d/dx sum(H(x) * g) = H(g)
+    xr = torch.randn(3, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    g = torch.randn(3, 256, device="cuda", dtype=torch.bfloat16)
+    y = torch.ops.b200ht.hadamard_transform(xr, 1.0 / 16)
+    y.backward(g)
+    ref = oracle.fwht_rows(g.double().cpu().numpy())
+    assert abs(xr.grad.double().cpu().numpy() - ref).max() <= 5e-2
+
+
+@pytest.mark.gpu
+def test_cuda_graph_capture_and_replay(pkg):
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(64, 4096, generator=g, device="cuda").bfloat16()
+    X = torch.randn(512, 1024, generator=g, device="cuda").bfloat16()
+    W = torch.randn(256, 1024, generator=g, device="cuda").bfloat16()
+    Wv = (torch.randn(512, 4096, generator=g, device="cuda") / 64).bfloat16()
+    Xv = torch.randn(4096, 4, generator=g, device="cuda").bfloat16()
+    expect = (pkg.hadamard_transform(x), pkg.fused_ht_gemm(X, W), pkg.fused_ht_gemv(Wv, Xv))
+    torch.cuda.synchronize()
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            got = (pkg.hadamard_transform(x), pkg.fused_ht_gemm(X, W), pkg.fused_ht_gemv(Wv, Xv))
+        for _ in range(3):
+            graph.replay()
+    torch.cuda.synchronize()
+    for a, b in zip(got, expect):
+        assert torch.equal(a, b)
+    assert pkg.device_status() == 0
