@@ -21,8 +21,10 @@ EXPORTS = (
     "b200ht_version",
     "b200ht_error_string",
     "b200ht_fwht",
+    "b200ht_fwht_signed",
     "b200ht_fused_gemm_workspace_bytes",
     "b200ht_fused_gemm",
+    "b200ht_fused_gemm_signed",
     "b200ht_fused_gemm_static",
     "b200ht_fused_gemv",
     "b200ht_device_status",
@@ -40,6 +42,10 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.b200ht_error_string.argtypes = [i]
     lib.b200ht_fwht.restype = i
     lib.b200ht_fwht.argtypes = [vp, vp, ctypes.c_uint64, ctypes.c_uint32, i, f, vp]
+    lib.b200ht_fwht_signed.restype = i
+    lib.b200ht_fwht_signed.argtypes = [vp, vp, ctypes.c_uint64, ctypes.c_uint32, i, f, vp, vp]
+    lib.b200ht_fused_gemm_signed.restype = i
+    lib.b200ht_fused_gemm_signed.argtypes = [vp, vp, vp, i, i, i, i, i, i, f, vp, vp, ctypes.c_size_t, vp]
     lib.b200ht_fused_gemm_workspace_bytes.restype = ctypes.c_size_t
     lib.b200ht_fused_gemm_workspace_bytes.argtypes = [i, i, i, i]
     lib.b200ht_fused_gemm.restype = i

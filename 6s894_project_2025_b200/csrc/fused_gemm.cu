@@ -11,7 +11,7 @@
 
 namespace b200ht {
 
-int launch_fwht(const void *in, void *out, uint64_t rows, uint32_t n, int dtype, float scale,
+int launch_fwht(const void *in, void *out, uint64_t rows, uint32_t n, int dtype, float scale, const void *signs,
                 cudaStream_t st);
 int launch_gemm_bf16_tcgen05(const void *Y, const void *W, void *C, int M, int N, int K, int out_dtype,
                              int out_layout, cudaStream_t st);
@@ -154,30 +154,48 @@ extern "C" size_t b200ht_fused_gemm_workspace_bytes(int M, int N, int K, int in_
     return (bytes + 255) & ~(size_t)255;
 }
 
-extern "C" int b200ht_fused_gemm(const void *X, const void *W, void *C, int M, int N, int K, int in_dtype,
-                                 int out_dtype, int out_layout, float scale, void *workspace,
-                                 size_t workspace_bytes, void *stream)
+static int fused_gemm_entry(const void *X, const void *W, void *C, int M, int N, int K, int in_dtype, int out_dtype,
+                            int out_layout, float scale, const void *signs, void *workspace, size_t workspace_bytes,
+                            void *stream)
 {
     using namespace b200ht;
     if (in_dtype != B200HT_F32 && in_dtype != B200HT_BF16) return B200HT_ERR_DTYPE;
     if (out_dtype != B200HT_F32 && out_dtype != B200HT_BF16) return B200HT_ERR_DTYPE;
+    if (signs && in_dtype != B200HT_BF16) return B200HT_ERR_DTYPE;
     if (out_layout != B200HT_OUT_MN && out_layout != B200HT_OUT_NM) return B200HT_ERR_SIZE;
     if (K < 2 || K > (1 << kMaxLogN) || !is_pow2((uint64_t)K)) return B200HT_ERR_SIZE;
     if (M < 0 || N < 0) return B200HT_ERR_SIZE;
     if (M == 0 || N == 0) return 0;
     if (!X || !W || !C) return B200HT_ERR_NULL;
-    if (!aligned16(X) || !aligned16(W) || !aligned16(C)) return B200HT_ERR_ALIGN;
+    if (!aligned16(X) || !aligned16(W) || !aligned16(C) || (signs && !aligned16(signs))) return B200HT_ERR_ALIGN;
     const size_t need = b200ht_fused_gemm_workspace_bytes(M, N, K, in_dtype);
     if (!workspace || workspace_bytes < need) return B200HT_ERR_WORKSPACE;
     if (((uintptr_t)workspace & 255u) != 0) return B200HT_ERR_ALIGN;
     int rc = check_device();
     if (rc) return rc;
     cudaStream_t st = (cudaStream_t)stream;
-    rc = launch_fwht(X, workspace, (uint64_t)N, (uint32_t)K, in_dtype, scale, st);
+    rc = launch_fwht(X, workspace, (uint64_t)N, (uint32_t)K, in_dtype, scale, signs, st);
     if (rc) return rc;
     if (in_dtype == B200HT_F32)
         return launch_sgemm((const float *)W, (const float *)workspace, C, M, N, K, out_dtype, out_layout, st);
     return launch_gemm_bf16_tcgen05(workspace, W, C, M, N, K, out_dtype, out_layout, st);
+}
+
+extern "C" int b200ht_fused_gemm(const void *X, const void *W, void *C, int M, int N, int K, int in_dtype,
+                                 int out_dtype, int out_layout, float scale, void *workspace,
+                                 size_t workspace_bytes, void *stream)
+{
+    return fused_gemm_entry(X, W, C, M, N, K, in_dtype, out_dtype, out_layout, scale, nullptr, workspace,
+                            workspace_bytes, stream);
+}
+
+extern "C" int b200ht_fused_gemm_signed(const void *X, const void *W, void *C, int M, int N, int K, int in_dtype,
+                                        int out_dtype, int out_layout, float scale, const void *signs,
+                                        void *workspace, size_t workspace_bytes, void *stream)
+{
+    if (!signs) return B200HT_ERR_NULL;
+    return fused_gemm_entry(X, W, C, M, N, K, in_dtype, out_dtype, out_layout, scale, signs, workspace,
+                            workspace_bytes, stream);
 }
 
 // ---------------------------------------------------------------------------

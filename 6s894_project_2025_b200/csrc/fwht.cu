@@ -25,6 +25,17 @@
 namespace b200ht {
 
 int launch_fwht_tc(const void *in, void *out, uint64_t rows, int logn, int dtype, float scale, cudaStream_t st);
+
+// Optional +-1 diagonal in front of the transform (randomised Hadamard transform): `signs` holds one 16-bit word
+// per column, 0x8000 where the column is negated, and is applied by flipping the sign bits of the loaded vector.
+__device__ __forceinline__ uint4 flip_signs(uint4 v, const uint4 *signs, uint32_t vec_in_row)
+{
+    if (signs) {
+        const uint4 m = __ldg(signs + vec_in_row);
+        v.x ^= m.x; v.y ^= m.y; v.z ^= m.z; v.w ^= m.w;
+    }
+    return v;
+}
 // Smallest log2(n) sent to the tcgen05 kernel; B200HT_FWHT_TC_MIN=<log2 n> overrides it (tuning knob).
 static int tc_min_logn()
 {
@@ -38,8 +49,8 @@ static int tc_min_logn()
 // A warp owns GRP consecutive 256-element chunks (GRP*32 16-byte vectors).
 // ---------------------------------------------------------------------------
 template <int DT, int LOGN>
-__global__ void __launch_bounds__(256) fwht_reg_kernel(const uint4 *in, uint4 *out,
-                                                       uint64_t total_vec, float mult)
+__global__ void __launch_bounds__(256) fwht_reg_kernel(const uint4 *in, uint4 *out, uint64_t total_vec,
+                                                       float mult, const uint4 *signs)
 {
     constexpr int P = LOGN < 8 ? LOGN : 8;
     constexpr int CPR = LOGN > 8 ? (1 << (LOGN - 8)) : 1;  // chunks per row
@@ -62,7 +73,8 @@ __global__ void __launch_bounds__(256) fwht_reg_kernel(const uint4 *in, uint4 *o
 #pragma unroll
     for (int g = 0; g < GRP; ++g) {
         const uint64_t idx = first + (uint64_t)g * 32 + lane;
-        v[g] = idx < total_vec ? ld_stream(in + idx) : make_uint4(0, 0, 0, 0);
+        v[g] = idx < total_vec ? flip_signs(ld_stream(in + idx), signs, (uint32_t)idx & ((1u << (LOGN - 3)) - 1u))
+                               : make_uint4(0, 0, 0, 0);
     }
     float o[GRP][8];
     rot8x<DT, GRP>(v, o, A1, A2);
@@ -116,7 +128,7 @@ struct SmemCfg {
 
 template <int DT, int LOGN>
 __global__ void __launch_bounds__(256) fwht_smem_kernel(const uint4 *in, uint4 *out, uint64_t rows,
-                                                        float mult)
+                                                        float mult, const uint4 *signs)
 {
     using Cfg = SmemCfg<LOGN>;
     constexpr int Q = Cfg::Q, CPR = Cfg::CPR;
@@ -142,7 +154,8 @@ __global__ void __launch_bounds__(256) fwht_smem_kernel(const uint4 *in, uint4 *
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int c = c0 + 8 * u;
-            v[u] = c < chunks_here ? ld_stream(gin + c * 32 + lane) : make_uint4(0, 0, 0, 0);
+            v[u] = c < chunks_here ? flip_signs(ld_stream(gin + c * 32 + lane), signs, (uint32_t)((c & (CPR - 1)) * 32 + lane))
+                                   : make_uint4(0, 0, 0, 0);
         }
         float o[U][8];
         rot8x<DT, U>(v, o, A1, A2);
@@ -243,7 +256,7 @@ struct Smem2Cfg {
 
 template <int DT, int LOGN>
 __global__ void __launch_bounds__(256) fwht_smem2_kernel(const uint4 *in, uint4 *out, uint64_t rows,
-                                                         float mult)
+                                                         float mult, const uint4 *signs)
 {
     using Cfg = Smem2Cfg<LOGN>;
     constexpr int CPR = Cfg::CPR, RB = Cfg::RB, SB = Cfg::SB, J = 1 << RB;
@@ -267,7 +280,8 @@ __global__ void __launch_bounds__(256) fwht_smem2_kernel(const uint4 *in, uint4 
         for (int g0 = warp * 4; g0 < chunks_here; g0 += 8 * 4) {
             uint4 v[4];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) v[u] = ld_stream(gin + (g0 + u) * 32 + lane);
+            for (int u = 0; u < 4; ++u)
+                v[u] = flip_signs(ld_stream(gin + (g0 + u) * 32 + lane), signs, (uint32_t)(((g0 + u) & (CPR - 1)) * 32 + lane));
             float o[4][8];
             rot8x<DT, 4>(v, o, A1, A2);
 #pragma unroll
@@ -358,13 +372,14 @@ __global__ void __launch_bounds__(256) fwht_smem2_kernel(const uint4 *in, uint4 
 // n = 2, 4 (16-bit): one thread per row.
 // ---------------------------------------------------------------------------
 template <int DT>
-__global__ void fwht_tiny_kernel(const uint16_t *in, uint16_t *out, uint64_t rows, int n, float scale)
+__global__ void fwht_tiny_kernel(const uint16_t *in, uint16_t *out, uint64_t rows, int n, float scale,
+                                 const uint16_t *signs)
 {
     const uint64_t r = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= rows) return;
     float v[4];
     for (int i = 0; i < n; ++i) {
-        const uint32_t u = in[r * n + i];
+        const uint32_t u = in[r * n + i] ^ (signs ? (uint32_t)signs[i] : 0u);
         v[i] = unpack2<DT>(u).x;
     }
     if (n == 2) {
@@ -400,7 +415,7 @@ __global__ void __launch_bounds__(256) fwht_f32_kernel(const float *in, float *o
 // host side
 // ---------------------------------------------------------------------------
 template <int DT, int LOGN>
-static int launch_reg(const void *in, void *out, uint64_t rows, float scale, cudaStream_t st)
+static int launch_reg(const void *in, void *out, uint64_t rows, float scale, const void *signs, cudaStream_t st)
 {
     constexpr int P = LOGN < 8 ? LOGN : 8;
     constexpr int CPR = LOGN > 8 ? (1 << (LOGN - 8)) : 1;
@@ -413,11 +428,11 @@ static int launch_reg(const void *in, void *out, uint64_t rows, float scale, cud
     // programmatic dependent launch: the small sizes are bound by launch latency, and this lets the scheduling
     // of back-to-back launches overlap (the kernel itself waits for its predecessors before touching memory)
     return launch_pdl(fwht_reg_kernel<DT, LOGN>, dim3((unsigned)blocks), dim3(256), 0, st, (const uint4 *)in,
-                      (uint4 *)out, total_vec, scale / f);
+                      (uint4 *)out, total_vec, scale / f, (const uint4 *)signs);
 }
 
 template <int DT, int LOGN>
-static int launch_smem(const void *in, void *out, uint64_t rows, float scale, cudaStream_t st)
+static int launch_smem(const void *in, void *out, uint64_t rows, float scale, const void *signs, cudaStream_t st)
 {
     using Cfg = SmemCfg<LOGN>;
     const uint64_t blocks = (rows + Cfg::SLAB_ROWS - 1) / Cfg::SLAB_ROWS;
@@ -426,11 +441,11 @@ static int launch_smem(const void *in, void *out, uint64_t rows, float scale, cu
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
     return launch_pdl(fwht_smem_kernel<DT, LOGN>, dim3((unsigned)blocks), dim3(256), (size_t)Cfg::SMEM_BYTES, st,
-                      (const uint4 *)in, (uint4 *)out, rows, scale * 64.0f);
+                      (const uint4 *)in, (uint4 *)out, rows, scale * 64.0f, (const uint4 *)signs);
 }
 
 template <int DT, int LOGN>
-static int launch_smem2(const void *in, void *out, uint64_t rows, float scale, cudaStream_t st)
+static int launch_smem2(const void *in, void *out, uint64_t rows, float scale, const void *signs, cudaStream_t st)
 {
     using Cfg = Smem2Cfg<LOGN>;
     const uint64_t blocks = (rows + Cfg::SLAB_ROWS - 1) / Cfg::SLAB_ROWS;
@@ -439,11 +454,12 @@ static int launch_smem2(const void *in, void *out, uint64_t rows, float scale, c
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
     return launch_pdl(fwht_smem2_kernel<DT, LOGN>, dim3((unsigned)blocks), dim3(256), (size_t)Cfg::SMEM_BYTES, st,
-                      (const uint4 *)in, (uint4 *)out, rows, scale * 16.0f);
+                      (const uint4 *)in, (uint4 *)out, rows, scale * 16.0f, (const uint4 *)signs);
 }
 
 template <int DT>
-static int launch_b16(const void *in, void *out, uint64_t rows, int logn, float scale, cudaStream_t st)
+static int launch_b16(const void *in, void *out, uint64_t rows, int logn, float scale, const void *signs,
+                      cudaStream_t st)
 {
     switch (logn) {
     case 1:
@@ -451,22 +467,22 @@ static int launch_b16(const void *in, void *out, uint64_t rows, int logn, float 
         const uint64_t blocks = (rows + 255) / 256;
         if (blocks > 0x7fffffffull) return B200HT_ERR_SIZE;
         fwht_tiny_kernel<DT><<<(unsigned)blocks, 256, 0, st>>>((const uint16_t *)in, (uint16_t *)out, rows,
-                                                              1 << logn, scale);
+                                                              1 << logn, scale, (const uint16_t *)signs);
         return (int)cudaGetLastError();
     }
-    case 3: return launch_reg<DT, 3>(in, out, rows, scale, st);
-    case 4: return launch_reg<DT, 4>(in, out, rows, scale, st);
-    case 5: return launch_reg<DT, 5>(in, out, rows, scale, st);
-    case 6: return launch_reg<DT, 6>(in, out, rows, scale, st);
-    case 7: return launch_reg<DT, 7>(in, out, rows, scale, st);
-    case 8: return launch_reg<DT, 8>(in, out, rows, scale, st);
-    case 9: return launch_reg<DT, 9>(in, out, rows, scale, st);
-    case 10: return launch_reg<DT, 10>(in, out, rows, scale, st);
-    case 11: return launch_reg<DT, 11>(in, out, rows, scale, st);
-    case 12: return launch_smem2<DT, 12>(in, out, rows, scale, st);
-    case 13: return launch_smem<DT, 13>(in, out, rows, scale, st);
-    case 14: return launch_smem<DT, 14>(in, out, rows, scale, st);
-    case 15: return launch_smem<DT, 15>(in, out, rows, scale, st);
+    case 3: return launch_reg<DT, 3>(in, out, rows, scale, signs, st);
+    case 4: return launch_reg<DT, 4>(in, out, rows, scale, signs, st);
+    case 5: return launch_reg<DT, 5>(in, out, rows, scale, signs, st);
+    case 6: return launch_reg<DT, 6>(in, out, rows, scale, signs, st);
+    case 7: return launch_reg<DT, 7>(in, out, rows, scale, signs, st);
+    case 8: return launch_reg<DT, 8>(in, out, rows, scale, signs, st);
+    case 9: return launch_reg<DT, 9>(in, out, rows, scale, signs, st);
+    case 10: return launch_reg<DT, 10>(in, out, rows, scale, signs, st);
+    case 11: return launch_reg<DT, 11>(in, out, rows, scale, signs, st);
+    case 12: return launch_smem2<DT, 12>(in, out, rows, scale, signs, st);
+    case 13: return launch_smem<DT, 13>(in, out, rows, scale, signs, st);
+    case 14: return launch_smem<DT, 14>(in, out, rows, scale, signs, st);
+    case 15: return launch_smem<DT, 15>(in, out, rows, scale, signs, st);
     }
     return B200HT_ERR_SIZE;
 }
@@ -485,10 +501,11 @@ int launch_fwht_f32(const float *in, float *out, uint64_t rows, int logn, float 
     return (int)cudaGetLastError();
 }
 
-int launch_fwht(const void *in, void *out, uint64_t rows, uint32_t n, int dtype, float scale,
+int launch_fwht(const void *in, void *out, uint64_t rows, uint32_t n, int dtype, float scale, const void *signs,
                 cudaStream_t st)
 {
     const int logn = ilog2(n);
+    if (dtype == B200HT_F32 && signs) return B200HT_ERR_DTYPE;  // the +-1 diagonal is implemented for 16-bit data
     if (dtype == B200HT_F32) return launch_fwht_f32((const float *)in, (float *)out, rows, logn, scale, st);
     // n = 32768: tcgen05 kernel (fwht_tcgen05.cu; needs 128-byte aligned pointers for TMA).  It is correct for
     // every n >= 256; B200HT_FWHT_TC_MIN=<log2 n> lowers the threshold, B200HT_FWHT_MMA_SYNC=1 disables it.
@@ -497,23 +514,24 @@ int launch_fwht(const void *in, void *out, uint64_t rows, uint32_t n, int dtype,
         const char *e = std::getenv("B200HT_FWHT_MMA_SYNC");
         return e && e[0] == '1';
     }();
-    if (logn >= kTcMinLogN && !use_mma_sync && ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 127u) == 0)
+    if (logn >= kTcMinLogN && !use_mma_sync && !signs && ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 127u) == 0)
         return launch_fwht_tc(in, out, rows, logn, dtype, scale, st);
-    if (dtype == B200HT_BF16) return launch_b16<B200HT_BF16>(in, out, rows, logn, scale, st);
-    return launch_b16<B200HT_F16>(in, out, rows, logn, scale, st);
+    if (dtype == B200HT_BF16) return launch_b16<B200HT_BF16>(in, out, rows, logn, scale, signs, st);
+    return launch_b16<B200HT_F16>(in, out, rows, logn, scale, signs, st);
 }
 
 }  // namespace b200ht
 
-extern "C" int b200ht_fwht(const void *in, void *out, uint64_t rows, uint32_t n, int dtype, float scale,
-                           void *stream)
+static int fwht_entry(const void *in, void *out, uint64_t rows, uint32_t n, int dtype, float scale, const void *signs,
+                      void *stream)
 {
     using namespace b200ht;
     if (dtype != B200HT_F16 && dtype != B200HT_BF16 && dtype != B200HT_F32) return B200HT_ERR_DTYPE;
+    if (signs && dtype == B200HT_F32) return B200HT_ERR_DTYPE;
     if (!is_pow2(n) || n < 2 || n > (1u << kMaxLogN)) return B200HT_ERR_SIZE;
     if (rows == 0) return 0;
     if (!in || !out) return B200HT_ERR_NULL;
-    if (!aligned16(in) || !aligned16(out)) return B200HT_ERR_ALIGN;
+    if (!aligned16(in) || !aligned16(out) || (signs && !aligned16(signs))) return B200HT_ERR_ALIGN;
     const uint64_t esz = dtype == B200HT_F32 ? 4 : 2;
     if (rows > (~0ull) / ((uint64_t)n * esz)) return B200HT_ERR_SIZE;
     const uint64_t bytes = rows * n * esz;
@@ -523,5 +541,18 @@ extern "C" int b200ht_fwht(const void *in, void *out, uint64_t rows, uint32_t n,
     }
     int rc = check_device();
     if (rc) return rc;
-    return launch_fwht(in, out, rows, n, dtype, scale, (cudaStream_t)stream);
+    return launch_fwht(in, out, rows, n, dtype, scale, signs, (cudaStream_t)stream);
+}
+
+extern "C" int b200ht_fwht(const void *in, void *out, uint64_t rows, uint32_t n, int dtype, float scale,
+                           void *stream)
+{
+    return fwht_entry(in, out, rows, n, dtype, scale, nullptr, stream);
+}
+
+extern "C" int b200ht_fwht_signed(const void *in, void *out, uint64_t rows, uint32_t n, int dtype, float scale,
+                                  const void *signs, void *stream)
+{
+    if (!signs) return B200HT_ERR_NULL;
+    return fwht_entry(in, out, rows, n, dtype, scale, signs, stream);
 }

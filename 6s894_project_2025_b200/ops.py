@@ -30,7 +30,19 @@ def _stream_ptr(device: torch.device) -> int:
     return int(torch.cuda.current_stream(device).cuda_stream)
 
 
-def hadamard_transform(x: torch.Tensor, inplace: bool = False, *, scale: float | None = None) -> torch.Tensor:
+def sign_mask(signs: torch.Tensor, n: int, device: torch.device) -> torch.Tensor:
+    """+-1 diagonal (length n, any real dtype) -> the 16-bit sign-bit table the library takes
+    (0x8000 where the entry is negative), padded to a whole 16-byte vector."""
+    if signs.dim() != 1 or int(signs.shape[0]) != n:
+        raise RuntimeError(f"signs must be a vector of length {n}")
+    m = torch.where(signs.to(device) < 0, -32768, 0).to(torch.int16)
+    if n < 8:
+        m = torch.cat([m, m.new_zeros(8 - n)])
+    return m.contiguous()
+
+
+def hadamard_transform(x: torch.Tensor, inplace: bool = False, *, scale: float | None = None,
+                       signs: torch.Tensor | None = None) -> torch.Tensor:
     """``x @ H_n * scale`` along the last dimension, H_n in Sylvester order.
 
     Same contract as ``csrc.hadamard_transform`` (csrc/hadamard_transform.cpp:12-70):
@@ -38,7 +50,9 @@ def hadamard_transform(x: torch.Tensor, inplace: bool = False, *, scale: float |
     <= 2**15; the result has the input's shape; with ``inplace=True`` the data
     of ``x`` is overwritten and ``x`` itself is returned, also when a temporary
     was needed.  ``scale`` defaults to the reference's ``1/sqrt(n)``.  Unlike
-    the reference, any n >= 2 and any number of rows is accepted.
+    the reference, any n >= 2 and any number of rows is accepted.  ``signs`` (a
+    vector of n entries, negative = flip) applies a +-1 diagonal to the columns
+    before the transform (randomised Hadamard transform) at no extra pass.
     """
     if x.dtype not in (torch.float16, torch.bfloat16):
         raise RuntimeError("Only fp16 and bf16 supported currently")
@@ -62,8 +76,13 @@ def hadamard_transform(x: torch.Tensor, inplace: bool = False, *, scale: float |
     rows = work.numel() // n
     if rows > 0:
         with torch.cuda.device(x.device):
-            rc = lib.b200ht_fwht(work.data_ptr(), out.data_ptr(), rows, n, _DT[x.dtype], float(scale),
-                                 _stream_ptr(x.device))
+            if signs is None:
+                rc = lib.b200ht_fwht(work.data_ptr(), out.data_ptr(), rows, n, _DT[x.dtype], float(scale),
+                                     _stream_ptr(x.device))
+            else:
+                mask = sign_mask(signs, n, x.device)
+                rc = lib.b200ht_fwht_signed(work.data_ptr(), out.data_ptr(), rows, n, _DT[x.dtype], float(scale),
+                                            mask.data_ptr(), _stream_ptr(x.device))
         _lib.check(rc, "b200ht_fwht")
     if inplace:
         if work is not x:
@@ -78,7 +97,8 @@ def fused_gemm_workspace_bytes(M: int, N: int, K: int, dtype: torch.dtype) -> in
 
 def fused_ht_gemm(X: torch.Tensor, W: torch.Tensor, *, scale: float | None = None,
                   out_dtype: torch.dtype | None = None, out_layout: str = "mn",
-                  out: torch.Tensor | None = None, workspace: torch.Tensor | None = None) -> torch.Tensor:
+                  out: torch.Tensor | None = None, workspace: torch.Tensor | None = None,
+                  signs: torch.Tensor | None = None) -> torch.Tensor:
     """C = W . H(X): ``C[m, t] = sum_k W[m, k] * (scale * H_K x_t)[k]``.
 
     ``X`` is (N tokens, K) token-major and ``W`` is (M, K) row-major, the
@@ -87,6 +107,7 @@ def fused_ht_gemm(X: torch.Tensor, W: torch.Tensor, *, scale: float | None = Non
     both bf16 (tensor cores, fp32 accumulate).  ``out_layout="mn"`` returns the
     reference's (M, N) matrix, ``"nm"`` the token-major (N, M) one.  ``scale``
     defaults to 1/sqrt(K); the reference executable computes ``scale=1.0``.
+    ``signs`` (K entries, negative = flip; bf16 inputs only) computes W . H(d * X).
     """
     if X.dtype != W.dtype or X.dtype not in (torch.float32, torch.bfloat16):
         raise RuntimeError("fused_ht_gemm: X and W must both be float32 or both bfloat16")
@@ -120,10 +141,17 @@ def fused_ht_gemm(X: torch.Tensor, W: torch.Tensor, *, scale: float | None = Non
         raise RuntimeError("fused_ht_gemm: workspace too small")
     if M > 0 and N > 0:
         with torch.cuda.device(X.device):
-            rc = lib.b200ht_fused_gemm(X.data_ptr(), W.data_ptr(), out.data_ptr(), M, N, K, _DT[X.dtype],
-                                       _DT[out_dtype], _lib.OUT_MN if out_layout == "mn" else _lib.OUT_NM,
-                                       float(scale), workspace.data_ptr(),
-                                       workspace.numel() * workspace.element_size(), _stream_ptr(X.device))
+            layout = _lib.OUT_MN if out_layout == "mn" else _lib.OUT_NM
+            wsb = workspace.numel() * workspace.element_size()
+            if signs is None:
+                rc = lib.b200ht_fused_gemm(X.data_ptr(), W.data_ptr(), out.data_ptr(), M, N, K, _DT[X.dtype],
+                                           _DT[out_dtype], layout, float(scale), workspace.data_ptr(), wsb,
+                                           _stream_ptr(X.device))
+            else:
+                mask = sign_mask(signs, K, X.device)
+                rc = lib.b200ht_fused_gemm_signed(X.data_ptr(), W.data_ptr(), out.data_ptr(), M, N, K, _DT[X.dtype],
+                                                  _DT[out_dtype], layout, float(scale), mask.data_ptr(),
+                                                  workspace.data_ptr(), wsb, _stream_ptr(X.device))
         _lib.check(rc, "b200ht_fused_gemm")
     return out
 

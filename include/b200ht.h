@@ -67,6 +67,18 @@ int b200ht_fwht(const void *in, void *out, uint64_t rows, uint32_t n, int dtype,
                 float scale, void *stream);
 
 /*
+ * Randomised Hadamard transform: out[r, :] = scale * (in[r, :] * d) . H_n with a +-1
+ * diagonal d in front of the transform.  `signs` holds n 16-bit words, 0x8000
+ * where d is -1 and 0 where it is +1 (16-byte aligned device memory); the kernel
+ * flips the sign bits of the loaded elements, so the option costs one cached
+ * 16-byte load per vector.  dtype F16 | BF16.  Everything else as b200ht_fwht.
+ * No counterpart in the reference, whose callers would multiply by d in a
+ * separate pass before csrc.hadamard_transform (bench/bench.py:79-81).
+ */
+int b200ht_fwht_signed(const void *in, void *out, uint64_t rows, uint32_t n, int dtype,
+                       float scale, const void *signs, void *stream);
+
+/*
  * Fused C = W . H(X):  C[m, t] = sum_k W[m, k] * (scale * H_K x_t)[k].
  *   X  N x K, token-major (X[t*K + k])           in_dtype  F32 | BF16
  *   W  M x K, row-major   (W[m*K + k])           in_dtype  (same as X)
@@ -86,6 +98,13 @@ size_t b200ht_fused_gemm_workspace_bytes(int M, int N, int K, int in_dtype);
 int b200ht_fused_gemm(const void *X, const void *W, void *C, int M, int N, int K,
                       int in_dtype, int out_dtype, int out_layout, float scale,
                       void *workspace, size_t workspace_bytes, void *stream);
+
+/* b200ht_fused_gemm with the +-1 diagonal of b200ht_fwht_signed applied to the
+ * tokens before the transform: C = W . H(d * X).  BF16 inputs only. */
+int b200ht_fused_gemm_signed(const void *X, const void *W, void *C, int M, int N, int K,
+                             int in_dtype, int out_dtype, int out_layout, float scale,
+                             const void *signs, void *workspace, size_t workspace_bytes,
+                             void *stream);
 
 /*
  * b200ht_fused_gemm without a caller-provided workspace and without any

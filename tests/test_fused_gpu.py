@@ -170,3 +170,14 @@ def test_host_pipeline_matches_single_call(pkg, oracle):
         torch.cuda.synchronize()
         assert torch.equal(out, ref)
     assert pkg.device_status() == 0
+
+
+def test_fused_gemm_with_sign_diagonal(pkg, oracle):
+    inp = oracle.make_inputs("c5", K=2048, M=300, N=260)
+    W, d = inp["W"], inp["d"]
+    X0 = torch.randn(260, 2048, generator=torch.Generator().manual_seed(9)).bfloat16()   # tokens before the diagonal
+    ref = oracle.fused_gemm_ref((X0.double() * d.double()).numpy(), W.double().numpy())
+    C = pkg.fused_ht_gemm(X0.cuda(), W.cuda(), signs=d)
+    _check(oracle, C.cpu().numpy(), ref, BF16_TOL)
+    C2 = pkg.fused_ht_gemm((X0 * d.bfloat16()).cuda(), W.cuda())
+    assert torch.equal(C, C2)

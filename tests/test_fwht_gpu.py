@@ -166,3 +166,18 @@ def test_tcgen05_kernel_all_sizes(lib, oracle, logn, dtype, atol):
     env = dict(os.environ, B200HT_FWHT_TC_MIN="8")
     r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=300)
     assert r.returncode == 0 and "ok" in r.stdout, r.stdout + r.stderr
+
+
+@pytest.mark.parametrize("n", [2, 4, 8, 64, 256, 1024, 4096, 8192, 32768])
+@pytest.mark.parametrize("dtype,atol", [(torch.float16, 1e-2), (torch.bfloat16, 5e-2)])
+def test_sign_diagonal_is_folded_into_the_transform(pkg, oracle, n, dtype, atol):
+    g = torch.Generator().manual_seed(n)
+    d = (2 * torch.randint(0, 2, (n,), generator=g) - 1).float()
+    x = torch.randn(7, n, generator=g).to(dtype)
+    ref = oracle.fwht_rows((x.double() * d.double()).numpy())
+    y = pkg.hadamard_transform(x.cuda(), signs=d)
+    assert np.max(np.abs(y.double().cpu().numpy() - ref)) <= atol
+    # identical to flipping the inputs first (sign flips are exact in 16 bit)
+    y2 = pkg.hadamard_transform((x * d.to(dtype)).cuda())
+    if n != 32768:   # 32768 without signs runs the tcgen05 kernel, whose rounding points differ
+        assert torch.equal(y, y2)
