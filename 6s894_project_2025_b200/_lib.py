@@ -28,6 +28,7 @@ EXPORTS = (
     "b200ht_fused_gemm_static",
     "b200ht_fused_gemv",
     "b200ht_device_status",
+    "b200ht_selftest_wait_timeout",
 )
 
 _lock = threading.Lock()
@@ -54,6 +55,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.b200ht_fused_gemm_static.argtypes = [vp, vp, vp, i, i, i, i, i, i, f, vp]
     lib.b200ht_fused_gemv.restype = i
     lib.b200ht_fused_gemv.argtypes = [vp, vp, vp, i, i, i, i, i, f, vp]
+    lib.b200ht_selftest_wait_timeout.restype = i
+    lib.b200ht_selftest_wait_timeout.argtypes = [ctypes.c_uint, vp]
     lib.b200ht_device_status.restype = i
     lib.b200ht_device_status.argtypes = [i]
 

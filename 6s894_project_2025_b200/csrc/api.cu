@@ -1,7 +1,7 @@
 // Version, error text, device check and the device status word.
 #include <mutex>
 
-#include "common.cuh"
+#include "tc_common.cuh"
 
 namespace b200ht {
 
@@ -72,4 +72,52 @@ extern "C" int b200ht_device_status(int clear)
         if (e != cudaSuccess) return (int)e;
     }
     return v;
+}
+
+// ---------------------------------------------------------------------------
+// Self-test of the bounded-wait mechanism that every mbarrier wait of the
+// tcgen05 / TMA kernels goes through: one thread waits on a barrier that nobody
+// will ever complete, with a caller-chosen limit.  The wait must give up, leave
+// B200HT_ERR_TIMEOUT in the device status word and the kernel must return, so
+// that the context stays usable.  Nothing faults, traps or hangs.
+// ---------------------------------------------------------------------------
+namespace b200ht {
+__global__ void wait_timeout_probe_kernel(unsigned long long limit_ns, int *status, int *gave_up)
+{
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        fence_barrier_init();
+        const bool ok = mbar_wait(smem_u32(&bar), 0u, &abort_flag, status, limit_ns);
+        *gave_up = ok ? 0 : 1;
+    }
+}
+}  // namespace b200ht
+
+namespace b200ht {
+__device__ int g_selftest_flag = 0;
+}
+
+extern "C" int b200ht_selftest_wait_timeout(unsigned int limit_us, void *stream)
+{
+    using namespace b200ht;
+    int rc = check_device();
+    if (rc) return rc;
+    if (limit_us == 0 || limit_us > 1000000u) return B200HT_ERR_SIZE;   // at most one second
+    int *flag = nullptr;
+    cudaError_t e = cudaGetSymbolAddress((void **)&flag, g_selftest_flag);
+    if (e != cudaSuccess) return (int)e;
+    cudaStream_t st = (cudaStream_t)stream;
+    e = cudaMemsetAsync(flag, 0, sizeof(int), st);
+    if (e != cudaSuccess) return (int)e;
+    wait_timeout_probe_kernel<<<1, 32, 0, st>>>((unsigned long long)limit_us * 1000ull, status_word_ptr(), flag);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    int gave_up = 0;
+    e = cudaMemcpyAsync(&gave_up, flag, sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return (int)e;
+    return gave_up ? B200HT_ERR_TIMEOUT : 0;
 }

@@ -45,7 +45,8 @@ __device__ __forceinline__ uint64_t global_ns()
 // on give-up; the caller then leaves its loop, the CTA drains and exits, and the
 // host finds B200HT_ERR_TIMEOUT in the device status word.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status,
+                                          uint64_t limit_ns = kWaitLimitNs)
 {
     if (mbar_test(bar, parity)) return true;
     const uint64_t t0 = global_ns();
@@ -54,7 +55,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (mbar_test(bar, parity)) return true;
         if ((++spins & 255u) == 0) {
             if (*abort_flag) return false;
-            if (global_ns() - t0 > kWaitLimitNs) {
+            if (global_ns() - t0 > limit_ns) {
                 *abort_flag = 1;
                 if (status) atomicExch(status, B200HT_ERR_TIMEOUT);
                 return false;

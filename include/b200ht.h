@@ -163,6 +163,16 @@ int b200ht_fused_gemv(const void *W, const void *X, void *Y, int M, int N, int B
  */
 int b200ht_device_status(int clear);
 
+/*
+ * Self-test of the time-limited waits used by the tcgen05 / TMA kernels: runs a
+ * one-thread kernel that waits, for at most `limit_us` microseconds (1 ..
+ * 1 000 000), on a barrier that is never completed.  Returns B200HT_ERR_TIMEOUT
+ * when the wait gave up as designed (the device status word then holds the same
+ * code; clear it with b200ht_device_status(1)), 0 if it did not, or a CUDA
+ * error.  Synchronises the stream.  No counterpart in the reference.
+ */
+int b200ht_selftest_wait_timeout(unsigned int limit_us, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

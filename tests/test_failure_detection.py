@@ -1,0 +1,59 @@
+"""Failure detection without a GPU fault: a wait that can never complete runs into its time limit, the kernel
+returns, the host reads B200HT_ERR_TIMEOUT, and the context keeps working.  The host-side half (a rank that
+never joins) runs as gloo ranks on the CPU."""
+import os
+import subprocess
+import sys
+import textwrap
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.mark.gpu
+def test_bounded_wait_gives_up_and_context_survives(pkg, lib):
+    l = lib.load()
+    assert l.b200ht_device_status(1) == 0
+    rc = l.b200ht_selftest_wait_timeout(2000, torch.cuda.current_stream().cuda_stream)   # 2 ms limit
+    assert rc == -8, lib.error_string(rc)
+    assert l.b200ht_device_status(1) == -8          # the kernel left the code in the status word ...
+    assert l.b200ht_device_status(0) == 0           # ... and clearing works
+    # the context is still usable: run a real kernel afterwards
+    x = torch.randn(8, 32768, device="cuda").bfloat16()
+    y = pkg.hadamard_transform(pkg.hadamard_transform(x))
+    assert (y.float() - x.float()).abs().max().item() < 0.2
+    assert pkg.device_status() == 0
+
+
+def test_missing_rank_is_detected_by_the_survivor(tmp_path):
+    """Two gloo ranks; rank 1 exits between steps (never joins the second gather).  Rank 0's collective ends with an
+    error after the short process-group timeout instead of hanging."""
+    script = tmp_path / "worker.py"
+    script.write_text(textwrap.dedent(f"""
+        import datetime, importlib, sys
+        sys.path.insert(0, {str(ROOT)!r})
+        import torch, torch.distributed as dist
+        pkg = importlib.import_module("6s894_project_2025_b200")
+        dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=5))
+        rank = dist.get_rank()
+        local = torch.full((3, 4), float(rank))
+        full = pkg.gather_result(local, 6, "nm")          # step 1: both ranks present
+        assert full.shape == (6, 4)
+        if rank == 1:
+            sys.exit(0)                                   # leaves between steps, nothing in flight
+        try:
+            pkg.gather_result(local, 6, "nm")             # step 2: the peer is gone
+        except Exception as e:                            # noqa: BLE001
+            print("survivor saw:", type(e).__name__)
+            sys.exit(0)
+        sys.exit(3)
+    """))
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="1")
+    r = subprocess.run(
+        [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+         "--master-addr", "127.0.0.1", "--master-port", "29633", str(script)],
+        capture_output=True, text=True, env=env, timeout=300)
+    assert "survivor saw:" in r.stdout + r.stderr, r.stdout + r.stderr
