@@ -10,7 +10,10 @@
 //   warp 1      allocates TMEM (512 columns = two 128 x 256 fp32 accumulators)
 //               and issues tcgen05.mma (M=128, N=256, K=16) from one thread
 //   warps 2..5  epilogue: tcgen05.ld of the finished accumulator, convert,
-//               store, while the next tile accumulates in the other TMEM half
+//               store, while the next tile accumulates in the other TMEM half.
+//               Token-major results are stored directly (a warp writes 32
+//               consecutive elements); M x N results are staged per warp in
+//               shared memory and written by TMA (32 rows x 128 bytes per op)
 // Every mbarrier wait is time-limited; on expiry the CTA drains and exits and
 // the device status word carries B200HT_ERR_TIMEOUT.
 #include <cstdlib>
@@ -31,7 +34,9 @@ struct TcCfg {
     static constexpr int A_BYTES = BM * TC_BK * 2;      // 16 / 32 KB
     static constexpr int B_BYTES = TC_BN * TC_BK * 2;   // 32 KB
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+    static constexpr int STORE_BUFS = MT == 1 ? 2 : 1;    // 4 KB staging buffers per epilogue warp (M x N layout)
+    static constexpr int STORE_BYTES = 4 * MT * STORE_BUFS * 4096;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STORE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
     static constexpr int NACC = MT == 1 ? 2 : 1;        // accumulator sets in TMEM
     static constexpr int THREADS = 64 + 128 * MT;       // TMA warp, MMA warp, 4 * MT epilogue warps
 };
@@ -99,21 +104,22 @@ __device__ __forceinline__ void tc_tile_coord(int tile, int mt, int nt, int &mb,
 
 template <int OUT_DT, int LAYOUT, int MT>
 __global__ void __launch_bounds__(TcCfg<MT>::THREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmY, void *C, int M,
-               int N, int K, int *status)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmY,
+               const __grid_constant__ CUtensorMap tmC, int tma_store, void *C, int M, int N, int K, int *status)
 {
     using Cfg = TcCfg<MT>;
     constexpr int STAGES = Cfg::STAGES, STAGE_BYTES = Cfg::STAGE_BYTES, NACC = Cfg::NACC;
     extern __shared__ unsigned char smem_dyn[];
     const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
-    const uint32_t bar_base = base + STAGES * STAGE_BYTES;
+    const uint32_t store_base = base + STAGES * STAGE_BYTES;   // 1024-byte aligned staging for the TMA-store epilogue
+    const uint32_t bar_base = store_base + Cfg::STORE_BYTES;
     // barriers: full[S], empty[S], tmem_full[2], tmem_empty[2]; then tmem address slot, abort flag
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
     auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
     auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
     unsigned char *gen_base = smem_dyn + (base - smem_u32(smem_dyn));
-    uint32_t *tmem_slot = (uint32_t *)(gen_base + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 4));
+    uint32_t *tmem_slot = (uint32_t *)(gen_base + STAGES * STAGE_BYTES + Cfg::STORE_BYTES + 8 * (2 * STAGES + 4));
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -137,6 +143,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // programmatic dependent launch: everything above overlapped the tail of the transform kernel that
+    // produces the token operand; from here on its output is needed
+    pdl_launch_dependents();
+    pdl_wait();
 
     const int mt = (M + Cfg::BM - 1) / Cfg::BM, nt = (N + TC_BN - 1) / TC_BN;
     const int ntiles = mt * nt;
@@ -218,17 +228,65 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (acc + h) * TC_BN;
             const int m = m0 + h * 128 + q * 32 + lane;
+            if (LAYOUT == B200HT_OUT_MN && tma_store) {
+                // M x N layout: a lane owns a row, so plain stores would scatter 16-byte pieces over 32 rows.
+                // Stage 32 rows x 128 bytes per warp in shared memory (128-byte swizzle) and let TMA write them.
+                constexpr int COLS = OUT_DT == B200HT_F32 ? 32 : 64;       // columns per 128-byte staging row
+                unsigned char *stage_gen = gen_base + STAGES * STAGE_BYTES + (warp - 2) * Cfg::STORE_BUFS * 4096;
+                const uint32_t stage_s = store_base + (uint32_t)((warp - 2) * Cfg::STORE_BUFS * 4096);
+                int sb = 0;
 #pragma unroll 1
-            for (int c = 0; c < TC_BN; c += 32) {
-                uint32_t r[32];
-                tmem_ld32(taddr + c, r);
-                tmem_ld_wait();
-                tc_store_chunk<OUT_DT, LAYOUT>(C, M, N, m, n0 + c, r);
+                for (int c = 0; c < TC_BN; c += COLS) {
+                    uint32_t r[32], r2[32];
+                    tmem_ld32(taddr + c, r);
+                    if (OUT_DT != B200HT_F32) tmem_ld32(taddr + c + 32, r2);
+                    tmem_ld_wait();
+                    // the buffer about to be overwritten must have been read by its previous store
+                    if (lane == 0) {
+                        if (Cfg::STORE_BUFS == 2) asm volatile("cp.async.bulk.wait_group.read 1;\n" ::: "memory");
+                        else asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
+                    }
+                    __syncwarp();
+                    unsigned char *row = stage_gen + sb * 4096 + lane * 128;
+#pragma unroll
+                    for (int v = 0; v < 8; ++v) {
+                        uint4 o;
+                        if (OUT_DT == B200HT_F32) {
+                            o = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+                        } else {
+                            const uint32_t *src = v < 4 ? r + 8 * v : r2 + 8 * (v - 4);
+                            o.x = pack2<B200HT_BF16>(__uint_as_float(src[0]), __uint_as_float(src[1]));
+                            o.y = pack2<B200HT_BF16>(__uint_as_float(src[2]), __uint_as_float(src[3]));
+                            o.z = pack2<B200HT_BF16>(__uint_as_float(src[4]), __uint_as_float(src[5]));
+                            o.w = pack2<B200HT_BF16>(__uint_as_float(src[6]), __uint_as_float(src[7]));
+                        }
+                        *(uint4 *)(row + ((v ^ (lane & 7)) << 4)) = o;
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) {
+                        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];\n" ::"l"(&tmC),
+                                     "r"(stage_s + (uint32_t)(sb * 4096)), "r"(n0 + c), "r"(m0 + h * 128 + q * 32)
+                                     : "memory");
+                        asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+                    }
+                    sb = (sb + 1) % Cfg::STORE_BUFS;
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < TC_BN; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(taddr + c, r);
+                    tmem_ld_wait();
+                    tc_store_chunk<OUT_DT, LAYOUT>(C, M, N, m, n0 + c, r);
+                }
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar(acc));
         }
+        if (LAYOUT == B200HT_OUT_MN && tma_store && lane == 0)
+            asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");   // this warp's stores are complete
     }
 
     tc_fence_before();
@@ -318,6 +376,22 @@ int encode_tmap_bf16_rows_chunks(CUtensorMap *map, const void *base, uint64_t ro
     return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
+// Output map for the TMA-store epilogue: rows x cols of fp32 or bf16, box = 32 rows x 128 bytes, 128-byte swizzle.
+static int encode_tmap_out_2d(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, int dtype)
+{
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return (int)cudaErrorNotSupported;
+    const uint64_t esz = dtype == B200HT_F32 ? 4 : 2;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * esz};
+    const cuuint32_t box[2] = {(cuuint32_t)(128 / esz), 32};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, dtype == B200HT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                    const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
 static int sm_count_tc()
 {
     int dev = 0, n = 148;
@@ -334,14 +408,20 @@ static int launch_tc_mt(const void *Y, const void *W, void *C, int M, int N, int
     if (rc) return rc;
     rc = encode_tmap_bf16_2d(&ty, Y, (uint64_t)N, (uint64_t)K, TC_BN);
     if (rc) return rc;
+    // M x N results go out through TMA (32 rows x 128 bytes per op) when rows of C are 16-byte multiples
+    CUtensorMap tc = tw;
+    int tma_store = 0;
+    if (LAYOUT == B200HT_OUT_MN) {
+        const uint64_t esz = OUT_DT == B200HT_F32 ? 4 : 2;
+        if (((uint64_t)N * esz) % 16 == 0 && encode_tmap_out_2d(&tc, C, (uint64_t)M, (uint64_t)N, OUT_DT) == 0) tma_store = 1;
+    }
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<OUT_DT, LAYOUT, MT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
     const int tiles = ((M + Cfg::BM - 1) / Cfg::BM) * ((N + TC_BN - 1) / TC_BN);
     const int grid = tiles < sm_count_tc() ? tiles : sm_count_tc();
-    gemm_tc_kernel<OUT_DT, LAYOUT, MT><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(tw, ty, C, M, N, K,
-                                                                                    status_word_ptr());
-    return (int)cudaGetLastError();
+    return launch_pdl(gemm_tc_kernel<OUT_DT, LAYOUT, MT>, dim3(grid), dim3(Cfg::THREADS), (size_t)Cfg::SMEM_BYTES, st,
+                      tw, ty, tc, tma_store, C, M, N, K, status_word_ptr());
 }
 
 template <int OUT_DT, int LAYOUT>
