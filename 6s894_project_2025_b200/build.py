@@ -32,6 +32,7 @@ NVCC_FLAGS = [
     "--expt-relaxed-constexpr",
     *(["-DB200HT_GEMV_TRACE"] if os.environ.get("B200HT_GEMV_TRACE") else []),  # developer timing hooks
     *(["-DB200HT_FWHT_TRACE"] if os.environ.get("B200HT_FWHT_TRACE") else []),
+    *os.environ.get("B200HT_NVCC_EXTRA", "").split(),  # developer experiments
     "-I", str(ROOT / "include"),
 ]
 

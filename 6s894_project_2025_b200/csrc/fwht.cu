@@ -28,13 +28,12 @@ int launch_fwht_tc(const void *in, void *out, uint64_t rows, int logn, int dtype
 
 // Optional +-1 diagonal in front of the transform (randomised Hadamard transform): `signs` holds one 16-bit word
 // per column, 0x8000 where the column is negated, and is applied by flipping the sign bits of the loaded vector.
-__device__ __forceinline__ uint4 flip_signs(uint4 v, const uint4 *signs, uint32_t vec_in_row)
+// The kernels take it as a template flag: in the unsigned instantiation the loads of a batch stay back to back,
+// which a run-time test between them would prevent.
+__device__ __forceinline__ void flip_signs(uint4 &v, const uint4 *signs, uint32_t vec_in_row)
 {
-    if (signs) {
-        const uint4 m = __ldg(signs + vec_in_row);
-        v.x ^= m.x; v.y ^= m.y; v.z ^= m.z; v.w ^= m.w;
-    }
-    return v;
+    const uint4 m = __ldg(signs + vec_in_row);
+    v.x ^= m.x; v.y ^= m.y; v.z ^= m.z; v.w ^= m.w;
 }
 // Smallest log2(n) sent to the tcgen05 kernel; B200HT_FWHT_TC_MIN=<log2 n> overrides it (tuning knob).
 static int tc_min_logn()
@@ -48,7 +47,7 @@ static int tc_min_logn()
 // n <= 2048, 16-bit: rows live in one warp's registers.
 // A warp owns GRP consecutive 256-element chunks (GRP*32 16-byte vectors).
 // ---------------------------------------------------------------------------
-template <int DT, int LOGN>
+template <int DT, int LOGN, bool SG>
 __global__ void __launch_bounds__(256) fwht_reg_kernel(const uint4 *in, uint4 *out, uint64_t total_vec,
                                                        float mult, const uint4 *signs)
 {
@@ -73,8 +72,14 @@ __global__ void __launch_bounds__(256) fwht_reg_kernel(const uint4 *in, uint4 *o
 #pragma unroll
     for (int g = 0; g < GRP; ++g) {
         const uint64_t idx = first + (uint64_t)g * 32 + lane;
-        v[g] = idx < total_vec ? flip_signs(ld_stream(in + idx), signs, (uint32_t)idx & ((1u << (LOGN - 3)) - 1u))
-                               : make_uint4(0, 0, 0, 0);
+        v[g] = idx < total_vec ? ld_stream(in + idx) : make_uint4(0, 0, 0, 0);
+    }
+    if constexpr (SG) {
+#pragma unroll
+        for (int g = 0; g < GRP; ++g) {
+            const uint64_t idx = first + (uint64_t)g * 32 + lane;
+            flip_signs(v[g], signs, (uint32_t)idx & ((1u << (LOGN - 3)) - 1u));
+        }
     }
     float o[GRP][8];
     rot8x<DT, GRP>(v, o, A1, A2);
@@ -126,7 +131,7 @@ struct SmemCfg {
     static constexpr int SMEM_BYTES = NCHUNK * 33 * 16;
 };
 
-template <int DT, int LOGN>
+template <int DT, int LOGN, bool SG>
 __global__ void __launch_bounds__(256) fwht_smem_kernel(const uint4 *in, uint4 *out, uint64_t rows,
                                                         float mult, const uint4 *signs)
 {
@@ -154,8 +159,11 @@ __global__ void __launch_bounds__(256) fwht_smem_kernel(const uint4 *in, uint4 *
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int c = c0 + 8 * u;
-            v[u] = c < chunks_here ? flip_signs(ld_stream(gin + c * 32 + lane), signs, (uint32_t)((c & (CPR - 1)) * 32 + lane))
-                                   : make_uint4(0, 0, 0, 0);
+            v[u] = c < chunks_here ? ld_stream(gin + c * 32 + lane) : make_uint4(0, 0, 0, 0);
+        }
+        if constexpr (SG) {
+#pragma unroll
+            for (int u = 0; u < U; ++u) flip_signs(v[u], signs, (uint32_t)(((c0 + 8 * u) & (CPR - 1)) * 32 + lane));
         }
         float o[U][8];
         rot8x<DT, U>(v, o, A1, A2);
@@ -254,7 +262,7 @@ struct Smem2Cfg {
     static constexpr int SB = Q - RB;                       // ... on the high lane bits
 };
 
-template <int DT, int LOGN>
+template <int DT, int LOGN, bool SG>
 __global__ void __launch_bounds__(256) fwht_smem2_kernel(const uint4 *in, uint4 *out, uint64_t rows,
                                                          float mult, const uint4 *signs)
 {
@@ -280,8 +288,11 @@ __global__ void __launch_bounds__(256) fwht_smem2_kernel(const uint4 *in, uint4 
         for (int g0 = warp * 4; g0 < chunks_here; g0 += 8 * 4) {
             uint4 v[4];
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
-                v[u] = flip_signs(ld_stream(gin + (g0 + u) * 32 + lane), signs, (uint32_t)(((g0 + u) & (CPR - 1)) * 32 + lane));
+            for (int u = 0; u < 4; ++u) v[u] = ld_stream(gin + (g0 + u) * 32 + lane);
+            if constexpr (SG) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) flip_signs(v[u], signs, (uint32_t)(((g0 + u) & (CPR - 1)) * 32 + lane));
+            }
             float o[4][8];
             rot8x<DT, 4>(v, o, A1, A2);
 #pragma unroll
@@ -427,8 +438,11 @@ static int launch_reg(const void *in, void *out, uint64_t rows, float scale, con
     const float f = hfrag_c(popc4(rot8_mask1(P))) * hfrag_c(popc4(rot8_mask2(P)));
     // programmatic dependent launch: the small sizes are bound by launch latency, and this lets the scheduling
     // of back-to-back launches overlap (the kernel itself waits for its predecessors before touching memory)
-    return launch_pdl(fwht_reg_kernel<DT, LOGN>, dim3((unsigned)blocks), dim3(256), 0, st, (const uint4 *)in,
-                      (uint4 *)out, total_vec, scale / f, (const uint4 *)signs);
+    if (signs)
+        return launch_pdl(fwht_reg_kernel<DT, LOGN, true>, dim3((unsigned)blocks), dim3(256), 0, st,
+                          (const uint4 *)in, (uint4 *)out, total_vec, scale / f, (const uint4 *)signs);
+    return launch_pdl(fwht_reg_kernel<DT, LOGN, false>, dim3((unsigned)blocks), dim3(256), 0, st, (const uint4 *)in,
+                      (uint4 *)out, total_vec, scale / f, (const uint4 *)nullptr);
 }
 
 template <int DT, int LOGN>
@@ -437,11 +451,13 @@ static int launch_smem(const void *in, void *out, uint64_t rows, float scale, co
     using Cfg = SmemCfg<LOGN>;
     const uint64_t blocks = (rows + Cfg::SLAB_ROWS - 1) / Cfg::SLAB_ROWS;
     if (blocks > 0x7fffffffull) return B200HT_ERR_SIZE;
-    cudaError_t e = cudaFuncSetAttribute(fwht_smem_kernel<DT, LOGN>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
-    if (e != cudaSuccess) return (int)e;
-    return launch_pdl(fwht_smem_kernel<DT, LOGN>, dim3((unsigned)blocks), dim3(256), (size_t)Cfg::SMEM_BYTES, st,
-                      (const uint4 *)in, (uint4 *)out, rows, scale * 64.0f, (const uint4 *)signs);
+    auto go = [&](auto kernel) -> int {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        return launch_pdl(kernel, dim3((unsigned)blocks), dim3(256), (size_t)Cfg::SMEM_BYTES, st, (const uint4 *)in,
+                          (uint4 *)out, rows, scale * 64.0f, (const uint4 *)signs);
+    };
+    return signs ? go(fwht_smem_kernel<DT, LOGN, true>) : go(fwht_smem_kernel<DT, LOGN, false>);
 }
 
 template <int DT, int LOGN>
@@ -450,11 +466,13 @@ static int launch_smem2(const void *in, void *out, uint64_t rows, float scale, c
     using Cfg = Smem2Cfg<LOGN>;
     const uint64_t blocks = (rows + Cfg::SLAB_ROWS - 1) / Cfg::SLAB_ROWS;
     if (blocks > 0x7fffffffull) return B200HT_ERR_SIZE;
-    cudaError_t e = cudaFuncSetAttribute(fwht_smem2_kernel<DT, LOGN>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
-    if (e != cudaSuccess) return (int)e;
-    return launch_pdl(fwht_smem2_kernel<DT, LOGN>, dim3((unsigned)blocks), dim3(256), (size_t)Cfg::SMEM_BYTES, st,
-                      (const uint4 *)in, (uint4 *)out, rows, scale * 16.0f, (const uint4 *)signs);
+    auto go = [&](auto kernel) -> int {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        return launch_pdl(kernel, dim3((unsigned)blocks), dim3(256), (size_t)Cfg::SMEM_BYTES, st, (const uint4 *)in,
+                          (uint4 *)out, rows, scale * 16.0f, (const uint4 *)signs);
+    };
+    return signs ? go(fwht_smem2_kernel<DT, LOGN, true>) : go(fwht_smem2_kernel<DT, LOGN, false>);
 }
 
 template <int DT>
