@@ -181,3 +181,34 @@ def test_fused_gemm_with_sign_diagonal(pkg, oracle):
     _check(oracle, C.cpu().numpy(), ref, BF16_TOL)
     C2 = pkg.fused_ht_gemm((X0 * d.bfloat16()).cuda(), W.cuda())
     assert torch.equal(C, C2)
+
+
+@pytest.mark.parametrize("dtype,out_dtype", [(torch.bfloat16, torch.bfloat16), (torch.float32, torch.float32)])
+@pytest.mark.parametrize("layout", ["mn", "nm"])
+def test_output_of_more_than_2_31_elements(pkg, dtype, out_dtype, layout):
+    """Output offsets past 2^31 elements: M x N = 65664 x 33000 (2.17e9 entries) with a small K.  Rows and
+    columns sampled across the whole output are compared with a torch product of the transformed tokens."""
+    M, N, K = 65664, 33000, 64
+    g = torch.Generator(device="cuda").manual_seed(11)
+    X = torch.randn(N, K, generator=g, device="cuda").to(dtype)
+    W = (torch.randn(M, K, generator=g, device="cuda") / 8).to(dtype)
+    C = pkg.fused_ht_gemm(X, W, out_dtype=out_dtype, out_layout=layout)
+    assert pkg.device_status() == 0
+    H = torch.ones(1, 1, dtype=torch.float64, device="cuda")
+    while H.shape[0] < K:
+        H = torch.cat([torch.cat([H, H], 1), torch.cat([H, -H], 1)], 0)
+    HX = (X.double() @ H * K ** -0.5).float()                    # explicit Sylvester matrix, as the reference's check
+    if dtype == torch.bfloat16:
+        HX = HX.bfloat16().float()                               # the kernel rounds H(X) to bf16 before the product
+    ref_full = lambda ms, ns: W[ms].double() @ HX[ns].double().t()
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    ms = torch.tensor(sorted({0, 1, 127, 128, M // 2, 65535, 65536, M - 1}), device="cuda")
+    ns = torch.tensor(sorted({0, 1, 255, 256, N // 2, 32767, 32768, N - 1}), device="cuda")
+    all_n = torch.arange(N, device="cuda")
+    all_m = torch.arange(M, device="cuda")
+    Cv = C if layout == "mn" else C.t()
+    for got, ref in ((Cv[ms].double(), ref_full(ms, all_n)), (Cv[:, ns].double(), ref_full(all_m, ns))):
+        err = (got - ref).norm() / ref.norm()
+        assert float(err) <= tol, float(err)
+    del C, Cv
+    torch.cuda.empty_cache()

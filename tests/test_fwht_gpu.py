@@ -181,3 +181,36 @@ def test_sign_diagonal_is_folded_into_the_transform(pkg, oracle, n, dtype, atol)
     y2 = pkg.hadamard_transform((x * d.to(dtype)).cuda())
     if n != 32768:   # 32768 without signs runs the tcgen05 kernel, whose rounding points differ
         assert torch.equal(y, y2)
+
+
+@pytest.mark.parametrize("n", [256, 2048, 4096, 8192, 32768])
+def test_more_than_2_31_elements(pkg, oracle, n):
+    """Element offsets past 2^31 (and byte offsets past 2^32): every kernel family of the 16-bit transform on an
+    8.6 GB buffer with a ragged row count.  Checked on rows sampled from both ends and the middle against the
+    oracle, and on the whole buffer through a checksum that the transform preserves: the first output of each
+    row is the row sum / sqrt(n)."""
+    rows = (1 << 31) // n + 5
+    g = torch.Generator(device="cuda").manual_seed(n)
+    x = torch.empty(rows, n, dtype=torch.bfloat16, device="cuda")
+    step = 1 << 14
+    for r0 in range(0, rows, step):   # filled in slices: no fp32 copy of the whole buffer
+        r1 = min(rows, r0 + step)
+        x[r0:r1] = torch.randn(r1 - r0, n, generator=g, device="cuda", dtype=torch.float32).bfloat16()
+    sample = sorted({0, 1, rows // 2, rows // 2 + 1, (1 << 31) // n - 1, (1 << 31) // n, rows - 2, rows - 1})
+    xin = x[sample].cpu()
+    row_sums = torch.empty(rows, dtype=torch.float32, device="cuda")
+    for r0 in range(0, rows, step):
+        r1 = min(rows, r0 + step)
+        row_sums[r0:r1] = x[r0:r1].float().sum(dim=1)
+    y = pkg.hadamard_transform(x, inplace=True)
+    assert y is x and pkg.device_status() == 0
+    ref = _ref(oracle, xin)
+    got = x[sample].double().cpu().numpy()
+    assert np.max(np.abs(got - ref)) <= 5e-2
+    assert oracle.rel_fro(got, ref) <= 2e-2
+    first = x[:, 0].float()
+    # |first - sum/sqrt(n)| <= bf16 rounding of a value of magnitude ~1 (sum of n N(0,1) / sqrt(n))
+    err = (first - row_sums * n ** -0.5).abs()
+    assert float(err.max()) <= 5e-2, float(err.max())
+    del x, row_sums
+    torch.cuda.empty_cache()
