@@ -127,104 +127,129 @@ gemv_bf16_kernel(const __nv_bfloat16 *W, const __nv_bfloat16 *X, void *Y, int M,
 //
 //  * From the first cycle the CTA streams its rows of W into a shared-memory
 //    ring with TMA tile loads (cp.async.bulk.tensor.3d over a [64 k][rows][N/64]
-//    view of W: one op brings all rows of a row group x 512..1024 k, 16-32 KB,
-//    as consecutive 128-byte-swizzled K-major tiles; completion is counted on an
+//    view of W: one op brings all rows of a row group x 256..1024 k as
+//    consecutive 128-byte-swizzled K-major tiles; completion is counted on an
 //    mbarrier per stage).  The copies hold no registers and no LSU slots, so HBM
 //    traffic runs underneath the transform of X and only pauses when the ring
-//    is full.  (Small ops starve the TMA engine: 1 KB per-row bulk copies and
-//    28-row x 128-byte boxes both stayed below 20 GB/s per SM.)
-//  * Meanwhile the warps copy X (N x B, b fastest) into shared memory and
-//    transform it there.  H(X) is kept per block of 8 columns as N vectors of
-//    16 bytes (vector k = columns 8cb..8cb+7 of row k): the columns are passenger
-//    bits, so X needs no transpose.  Each pass sends five index bits through
-//    rot8 on the lanes (identity on the three in-vector bits) and up to two more
-//    through fp32 register butterflies.
-//  * Then the warps consume the ring: ldmatrix of a 16-row x 16-k block of W (A
-//    operand), ldmatrix.trans of the matching 16 vectors of H(X) (B operand),
-//    mma.sync m16n8k16 with fp32 accumulators.  A warp owns one 16-row tile of
-//    the row group and every (16/tiles)-th k step, keeps its partial sums in
-//    registers over the whole K range, and the warps reduce through shared
-//    memory once per row group.  A stage is refilled one iteration after it was
-//    consumed, when all warps have released it.
-// Vector k of H(X) lives at position k ^ f(k) (low three bits only) so that
-// the contiguous accesses of the first pass, the 512-byte-strided accesses of
-// later passes and the eight row addresses of each ldmatrix are conflict free.
+//    is full.
+//  * Meanwhile the warps transpose X (N x B, b fastest) into shared memory as
+//    one row of N bf16 per column (row pitch N*2+16 bytes) and transform the
+//    rows there, so the cost of the transform follows the number of columns:
+//    pass A sends the low eight index bits of each 256-element chunk through
+//    rot8 (tensor cores) and up to two more through fp32 register butterflies;
+//    pass B finishes the remaining (at most three) bits with fp32 butterflies
+//    over 16-byte vectors.
+//  * Then the warps consume the ring in four groups of four warps.  A group
+//    takes whole ring items (every fourth), so four items are in work at the
+//    same time and the fixed cost of an item (barrier wait, release) is spread
+//    over eight k steps per warp.  Per k step a warp loads the 16 x 16 blocks of
+//    both row tiles with ldmatrix (A operand), the matching H(X) values with two
+//    32-bit loads per column tile (B operand: column g, k = 2t.. and 2t+8..) and
+//    issues mma.sync m16n8k16 with fp32 accumulators kept over the whole K
+//    range.  Warps release a stage through a shared counter and the last one to
+//    do so refills it at once, so no warp waits for another; the partial sums
+//    are reduced through shared memory once per row group.
+// The row pitch of H(X) puts column g+1 four banks after column g, so the 32
+// lanes of a B-operand load (8 columns x 4 k pairs) hit 32 different banks.
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ int hx_pos(int k) { return k ^ (((k >> 3) & 3) << 1) ^ ((k >> 5) & 7); }
-
 constexpr int GV_WARPS = 16;
 constexpr int GV_THREADS = GV_WARPS * 32;
+constexpr int GV_GROUPS = 4;                         // warp groups of the consume phase
+constexpr int GV_GW = GV_WARPS / GV_GROUPS;          // warps per group
 constexpr int GV_MAX_GROUP_ROWS = 32;                // rows of W per ring stage (one or two 16-row tiles)
 
-// One in-place pass over index bits [lo, lo+nb) (lanes, through rot8) and
-// [lo+nb, lo+nb+JB) (registers) of every 8-column block.  With nb < 5 the spare
-// lane bits carry the lowest index bits as passengers.  TPI tasks are kept in
-// flight per warp so that the mma latencies overlap.
-template <int JB, int TPI>
-__device__ __forceinline__ void hx_pass(uint4 *hx, int nplanes, int logn, int lo, int nb, float mult, int warp,
-                                        int lane)
+__host__ __device__ constexpr int hxt_pitch(int N) { return N * 2 + 16; }   // bytes per column of H(X)
+
+// Pass A of the in-place transform: index bits 0..7 (rot8) and 8..8+RB-1 (registers) of every group of
+// GRP = 2^RB consecutive 256-element chunks; `mult` is applied to the result.
+template <int RB>
+__device__ __forceinline__ void hxt_pass_a(unsigned char *hxT, int cols, int pitch, int logn, float mult, int warp,
+                                           int lane)
 {
-    constexpr int J = 1 << JB;
-    constexpr int CNT = TPI * J;
-    const int idb = 5 - nb;
-    const int k_lane = ((lane & ((1 << nb) - 1)) << lo) | (lane >> nb);
-    const int tl_bits = lo - idb;
-    const int hi = lo + nb + JB;
-    const int pp_shift = logn - 5 - JB;
-    const int ntasks = nplanes << pp_shift;
+    constexpr int GRP = 1 << RB;
     uint32_t A1[4], A2[4];
-    const unsigned m1 = (nb > 0 ? 2u : 0u) | (nb > 1 ? 4u : 0u);
-    const unsigned m2 = (nb > 2 ? 1u : 0u) | (nb > 3 ? 2u : 0u) | (nb > 4 ? 4u : 0u);
-    make_hfrag<B200HT_BF16>(A1, lane, m1, hfrag_c(popc4(m1)));
-    make_hfrag<B200HT_BF16>(A2, lane, m2, hfrag_c(popc4(m2)));
-    for (int task0 = warp; task0 < ntasks; task0 += GV_WARPS * TPI) {
-        uint4 *ptr[CNT];
-        uint4 v[CNT];
-        float o[CNT][8];
+    constexpr unsigned M1 = rot8_mask1(8), M2 = rot8_mask2(8);
+    make_hfrag<B200HT_BF16>(A1, lane, M1, hfrag_c(popc4(M1)));
+    make_hfrag<B200HT_BF16>(A2, lane, M2, hfrag_c(popc4(M2)));
+    const int gpr = 1 << (logn - 8 - RB);            // chunk groups per column
+    const int ntasks = cols * gpr;
+    for (int task = warp; task < ntasks; task += GV_WARPS) {
+        const int col = task / gpr, gi = task - col * gpr;
+        uint4 *base = (uint4 *)(hxT + (size_t)col * pitch) + (size_t)gi * (GRP * 32) + lane;
+        uint4 v[GRP];
 #pragma unroll
-        for (int q = 0; q < TPI; ++q) {
-            const int task = task0 + q * GV_WARPS;
-            const int tk = task < ntasks ? task : task0;
-            const int plane = tk >> pp_shift, tt = tk & ((1 << pp_shift) - 1);
-            const int k0 = ((tt & ((1 << tl_bits) - 1)) << idb) | ((tt >> tl_bits) << hi) | k_lane;
-            uint4 *base = hx + ((size_t)plane << logn);
+        for (int u = 0; u < GRP; ++u) v[u] = base[u * 32];
+        float o[GRP][8];
+        rot8x<B200HT_BF16, GRP>(v, o, A1, A2);
 #pragma unroll
-            for (int j = 0; j < J; ++j) ptr[q * J + j] = base + hx_pos(k0 | (j << (lo + nb)));
-        }
+        for (int s = 1; s < GRP; s <<= 1) {
 #pragma unroll
-        for (int i = 0; i < CNT; ++i) v[i] = *ptr[i];
-        rot8x<B200HT_BF16, CNT>(v, o, A1, A2);
+            for (int u = 0; u < GRP; ++u) {
+                if (!(u & s)) {
 #pragma unroll
-        for (int q = 0; q < TPI; ++q) {
-#pragma unroll
-            for (int s = 1; s < J; s <<= 1) {
-#pragma unroll
-                for (int j = 0; j < J; ++j) {
-                    if (!(j & s)) {
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) {
-                            const float x = o[q * J + j][e], y = o[q * J + (j | s)][e];
-                            o[q * J + j][e] = x + y;
-                            o[q * J + (j | s)][e] = x - y;
-                        }
+                    for (int e = 0; e < 8; ++e) {
+                        const float x = o[u][e], y = o[u | s][e];
+                        o[u][e] = x + y;
+                        o[u | s][e] = x - y;
                     }
                 }
             }
-            if (task0 + q * GV_WARPS < ntasks) {
+        }
 #pragma unroll
-                for (int j = 0; j < J; ++j) {
-                    const float *oo = o[q * J + j];
-                    uint4 r;
-                    r.x = pack2<B200HT_BF16>(oo[0] * mult, oo[1] * mult);
-                    r.y = pack2<B200HT_BF16>(oo[2] * mult, oo[3] * mult);
-                    r.z = pack2<B200HT_BF16>(oo[4] * mult, oo[5] * mult);
-                    r.w = pack2<B200HT_BF16>(oo[6] * mult, oo[7] * mult);
-                    *ptr[q * J + j] = r;
+        for (int u = 0; u < GRP; ++u) {
+            uint4 r;
+            r.x = pack2<B200HT_BF16>(o[u][0] * mult, o[u][1] * mult);
+            r.y = pack2<B200HT_BF16>(o[u][2] * mult, o[u][3] * mult);
+            r.z = pack2<B200HT_BF16>(o[u][4] * mult, o[u][5] * mult);
+            r.w = pack2<B200HT_BF16>(o[u][6] * mult, o[u][7] * mult);
+            base[u * 32] = r;
+        }
+    }
+}
+
+// Pass B: the top JB index bits, as fp32 butterflies over 2^JB vectors that sit 2^(logn-JB) elements apart.
+template <int JB>
+__device__ __forceinline__ void hxt_pass_b(unsigned char *hxT, int cols, int pitch, int logn, float mult, int tid)
+{
+    constexpr int J = 1 << JB;
+    const int vps = 1 << (logn - JB - 3);            // vectors per sub-block
+    const int ntasks = cols * vps;
+    for (int task = tid; task < ntasks; task += GV_THREADS) {
+        const int col = task / vps, p = task - col * vps;
+        uint4 *base = (uint4 *)(hxT + (size_t)col * pitch) + p;
+        float o[J][8];
+#pragma unroll
+        for (int j = 0; j < J; ++j) {
+            const uint4 v = base[(size_t)j * vps];
+            const float2 a = unpack2<B200HT_BF16>(v.x), b = unpack2<B200HT_BF16>(v.y),
+                         c = unpack2<B200HT_BF16>(v.z), d = unpack2<B200HT_BF16>(v.w);
+            o[j][0] = a.x; o[j][1] = a.y; o[j][2] = b.x; o[j][3] = b.y;
+            o[j][4] = c.x; o[j][5] = c.y; o[j][6] = d.x; o[j][7] = d.y;
+        }
+#pragma unroll
+        for (int s = 1; s < J; s <<= 1) {
+#pragma unroll
+            for (int j = 0; j < J; ++j) {
+                if (!(j & s)) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const float x = o[j][e], y = o[j | s][e];
+                        o[j][e] = x + y;
+                        o[j | s][e] = x - y;
+                    }
                 }
             }
         }
+#pragma unroll
+        for (int j = 0; j < J; ++j) {
+            uint4 r;
+            r.x = pack2<B200HT_BF16>(o[j][0] * mult, o[j][1] * mult);
+            r.y = pack2<B200HT_BF16>(o[j][2] * mult, o[j][3] * mult);
+            r.z = pack2<B200HT_BF16>(o[j][4] * mult, o[j][5] * mult);
+            r.w = pack2<B200HT_BF16>(o[j][6] * mult, o[j][7] * mult);
+            base[(size_t)j * vps] = r;
+        }
     }
-    __syncthreads();
 }
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t saddr)
@@ -233,11 +258,11 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t saddr)
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                  : "r"(saddr));
 }
-__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t (&r)[2], uint32_t saddr)
+__device__ __forceinline__ uint32_t lds32(uint32_t saddr)
 {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n"
-                 : "=r"(r[0]), "=r"(r[1])
-                 : "r"(saddr));
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(v) : "r"(saddr));
+    return v;
 }
 #ifdef B200HT_GEMV_TRACE
 __device__ unsigned long long g_gemv_trace[16];
@@ -256,29 +281,30 @@ gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bflo
     // ring first (1024-byte aligned stages for the 128-byte swizzle), then H(X), reduction buffer, barriers
     const uint32_t ring_s = (smem_u32(smem_dyn) + 1023u) & ~1023u;
     unsigned char *gen = smem_dyn + (ring_s - smem_u32(smem_dyn));
-    uint4 *hx = (uint4 *)(gen + (size_t)nstages * stage_bytes);                 // [NT][N] vectors
-    float *red = (float *)((unsigned char *)hx + (size_t)NT * N * 16);           // [16 warps][16][NT*8]
-    unsigned char *bar_mem = (unsigned char *)(red + GV_WARPS * 16 * NT * 8);    // full[], empty[], abort flag
+    const int pitch = hxt_pitch(N);
+    unsigned char *hxT = gen + (size_t)nstages * stage_bytes;                     // [Bg][pitch]
+    float *red = (float *)(hxT + (((size_t)Bg * pitch + 127) & ~(size_t)127));    // [8 warps][32 rows][NT*8]
+    unsigned char *bar_mem = (unsigned char *)(red + (GV_WARPS / 2) * 32 * NT * 8);  // full[], counters, abort flag
     const uint32_t bar_s = smem_u32(bar_mem);
+    int *released = (int *)(bar_mem + 8 * nstages);                               // warps done with stage s
     volatile int *abort_flag = (volatile int *)(bar_mem + 16 * nstages);
     auto full_bar = [&](int s) { return bar_s + 8u * s; };
-    auto empty_bar = [&](int s) { return bar_s + 8u * (nstages + s); };
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     GV_TRACE(0);
 
-    // rows of W owned by this CTA, in groups of group_rows; one ring item = (group, 256-k chunk)
+    // rows of W owned by this CTA, in groups of group_rows; one ring item = (group, 64*kc-wide k chunk)
     const int row_begin = blockIdx.x * rows_per_cta;
     const int row_end = (row_begin + rows_per_cta) < M ? (row_begin + rows_per_cta) : M;
     const int my_rows = row_end > row_begin ? row_end - row_begin : 0;
     const int ngroups = (my_rows + group_rows - 1) / group_rows;
-    const int nchunks = (N / 64) / kc;     // ring items per row group: kc 64-k chunks each
+    const int nchunks = (N / 64) / kc;     // ring items per row group
     const int total_items = ngroups * nchunks;
 
     if (tid == 0) {
         for (int s = 0; s < nstages; ++s) {
             mbar_init(full_bar(s), 1);
-            mbar_init(empty_bar(s), GV_WARPS);
+            released[s] = 0;
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -289,152 +315,190 @@ gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bflo
     pdl_launch_dependents();
     pdl_wait();
 
-    // one TMA op per ring item: group_rows x (64*kc) elements of W
+    // one TMA op per ring item: group_rows x (64*kc) elements of W (issued by one thread)
     auto issue = [&](int item) {
-        if (tid == 0) {
-            const int s = item % nstages;
-            const int grp = item / nchunks, chunk = item - grp * nchunks;
-            mbar_expect_tx(full_bar(s), (uint32_t)(group_rows * kc * 128));
-            tma_load_3d(ring_s + (uint32_t)(s * stage_bytes), &tmW, 0, row_begin + grp * group_rows, chunk * kc,
-                        full_bar(s));
-        }
+        const int s = item % nstages;
+        const int grp = item / nchunks, chunk = item - grp * nchunks;
+        mbar_expect_tx(full_bar(s), (uint32_t)(group_rows * kc * 128));
+        tma_load_3d(ring_s + (uint32_t)(s * stage_bytes), &tmW, 0, row_begin + grp * group_rows, chunk * kc,
+                    full_bar(s));
     };
-    const int prologue = total_items < nstages ? total_items : nstages;
-    for (int item = 0; item < prologue; ++item) issue(item);
+    if (tid == 0) {
+        const int prologue = total_items < nstages ? total_items : nstages;
+        for (int item = 0; item < prologue; ++item) issue(item);
+    }
     GV_TRACE(1);
 
-    // ------------------------------ H(X) into shared memory ------------------------------
-    if ((B & 7) == 0 && (b0 & 7) == 0 && (Bg & 7) == 0) {
+    // ------------------------------ X^T into shared memory ------------------------------
+    if (B == 1) {
         const uint4 *Xv = (const uint4 *)X;
-        const int vpr = B >> 3, v0 = b0 >> 3;
-#pragma unroll 4
-        for (int idx = tid; idx < NT * N; idx += GV_THREADS) {
-            const int k = idx / NT, cb = idx - k * NT;
-            hx[((size_t)cb << logn) + hx_pos(k)] = __ldg(Xv + (size_t)k * vpr + v0 + cb);
-        }
-    } else if (NT == 1 && b0 == 0 && Bg == B && (B == 1 || B == 2 || B == 4)) {
-        // 16 bytes of X hold 8/B consecutive rows k: one load, 8/B vectors (columns >= B are zero)
+        for (int v = tid; v < N / 8; v += GV_THREADS) ((uint4 *)hxT)[v] = __ldg(Xv + v);
+    } else if ((B & 7) == 0 && (b0 & 7) == 0 && (Bg & 7) == 0) {
+        // two rows k, k+1 of one block of 8 columns per thread: two 16-byte loads, eight 4-byte stores
         const uint4 *Xv = (const uint4 *)X;
-        const int kpv = 8 / B;
-        for (int v = tid; v < N / kpv; v += GV_THREADS) {
-            const uint4 x = __ldg(Xv + v);
-            const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+        const int vpr = B >> 3, v0 = b0 >> 3, nb8 = Bg >> 3;
+        for (int idx = tid; idx < (N / 2) * nb8; idx += GV_THREADS) {
+            const int kp = idx / nb8, cb = idx - kp * nb8;
+            const uint4 x0 = __ldg(Xv + (size_t)(2 * kp) * vpr + v0 + cb);
+            const uint4 x1 = __ldg(Xv + (size_t)(2 * kp + 1) * vpr + v0 + cb);
+            const uint32_t w0[4] = {x0.x, x0.y, x0.z, x0.w}, w1[4] = {x1.x, x1.y, x1.z, x1.w};
+            unsigned char *dst = hxT + (size_t)(cb * 8) * pitch + kp * 4;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                if (j < kpv) {
-                    uint4 r = make_uint4(0, 0, 0, 0);
-                    if (B == 1) r.x = (w[j >> 1] >> ((j & 1) * 16)) & 0xffffu;
-                    else if (B == 2) r.x = w[j];
-                    else { r.x = w[2 * j]; r.y = w[2 * j + 1]; }
-                    hx[hx_pos(v * kpv + j)] = r;
-                }
+            for (int j = 0; j < 4; ++j) {
+                *(uint32_t *)(dst + (size_t)(2 * j) * pitch) = __byte_perm(w0[j], w1[j], 0x5410);
+                *(uint32_t *)(dst + (size_t)(2 * j + 1) * pitch) = __byte_perm(w0[j], w1[j], 0x7632);
             }
         }
     } else {
         const unsigned short *Xs = (const unsigned short *)X;
-#pragma unroll 2
-        for (int idx = tid; idx < NT * N; idx += GV_THREADS) {
-            const int k = idx / NT, cb = idx - k * NT;
-            uint32_t h[8];
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                const int col = cb * 8 + c;
-                h[c] = col < Bg ? (uint32_t)__ldg(Xs + (size_t)k * B + b0 + col) : 0u;
-            }
-            hx[((size_t)cb << logn) + hx_pos(k)] =
-                make_uint4(h[0] | (h[1] << 16), h[2] | (h[3] << 16), h[4] | (h[5] << 16), h[6] | (h[7] << 16));
+        for (int idx = tid; idx < (N / 2) * Bg; idx += GV_THREADS) {
+            const int kp = idx / Bg, c = idx - kp * Bg;
+            const uint32_t lo = __ldg(Xs + (size_t)(2 * kp) * B + b0 + c), hi = __ldg(Xs + (size_t)(2 * kp + 1) * B + b0 + c);
+            *(uint32_t *)(hxT + (size_t)c * pitch + kp * 4) = lo | (hi << 16);
         }
     }
     __syncthreads();
     GV_TRACE(2);
     {
-        int lo = 0, rem = logn;
-        float applied = 1.f;  // power-of-two factors baked into the A fragments so far
-        while (rem > 0) {
-            int nb, jb;
-            if (lo == 0 || rem > 7) { nb = 5; jb = 0; }
-            else { nb = rem < 5 ? rem : 5; jb = rem - nb; }
-            const unsigned m1 = (nb > 0 ? 2u : 0u) | (nb > 1 ? 4u : 0u);
-            const unsigned m2 = (nb > 2 ? 1u : 0u) | (nb > 3 ? 2u : 0u) | (nb > 4 ? 4u : 0u);
-            applied *= hfrag_c(popc4(m1)) * hfrag_c(popc4(m2));
-            const float mult = (rem - nb - jb) == 0 ? scale / applied : 1.f;
-            if (jb == 0) hx_pass<0, 4>(hx, NT, logn, lo, nb, mult, warp, lane);
-            else if (jb == 1) hx_pass<1, 2>(hx, NT, logn, lo, nb, mult, warp, lane);
-            else hx_pass<2, 1>(hx, NT, logn, lo, nb, mult, warp, lane);
-            lo += nb + jb;
-            rem -= nb + jb;
-        }
+        // pass A covers 8 + ra bits, pass B the remaining jb (N <= 8192: jb <= 3)
+        const int ra = logn - 8 < 2 ? logn - 8 : 2;
+        const int jb = logn - 8 - ra;
+        constexpr float fa = hfrag_c(popc4(rot8_mask1(8))) * hfrag_c(popc4(rot8_mask2(8)));
+        const float mult_a = jb == 0 ? scale / fa : 1.f;
+        if (ra == 0) hxt_pass_a<0>(hxT, Bg, pitch, logn, mult_a, warp, lane);
+        else if (ra == 1) hxt_pass_a<1>(hxT, Bg, pitch, logn, mult_a, warp, lane);
+        else hxt_pass_a<2>(hxT, Bg, pitch, logn, mult_a, warp, lane);
+        __syncthreads();
+        if (jb == 1) hxt_pass_b<1>(hxT, Bg, pitch, logn, scale / fa, tid);
+        else if (jb == 2) hxt_pass_b<2>(hxT, Bg, pitch, logn, scale / fa, tid);
+        else if (jb == 3) hxt_pass_b<3>(hxT, Bg, pitch, logn, scale / fa, tid);
+        if (jb) __syncthreads();
     }
     GV_TRACE(3);
 
     // ------------------------------ consume the ring ------------------------------
     const int g = lane >> 2, t = lane & 3;
-    const uint32_t hx_s = smem_u32(hx);
-    // row tiles per group (1 or 2) and this warp's share: one tile, every kstride-th k step
-    const int rt = group_rows > 16 ? 2 : 1;
-    const int my_tile = warp & (rt - 1);
-    const int kstride = GV_WARPS / rt, kphase = warp / rt;
-    // ldmatrix (A): lane -> (row, 16-byte k chunk) of the 16 x 16 block, 128-byte swizzle of the TMA tile
-    const int a_row = my_tile * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+    const uint32_t hx_s = smem_u32(hxT);
+    const int rt = group_rows > 16 ? 2 : 1;               // 16-row tiles per row group
+    const int wg = warp / GV_GW, wj = warp - wg * GV_GW;   // warp group, warp within the group
+    // ldmatrix (A): lane -> (row, 16-byte k chunk) of a 16 x 16 block, 128-byte swizzle of the TMA tile
+    const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8;
     const int a_chunk = lane >> 4;
+    // B operand: column nt*8+g of H(X) (zero beyond Bg), k pairs 2t and 2t+8 of the k step
+    uint32_t b_addr[NT];
+    bool b_ok[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        const int col = nt * 8 + g;
+        b_ok[nt] = col < Bg;
+        b_addr[nt] = hx_s + (uint32_t)((b_ok[nt] ? col : 0) * pitch) + (uint32_t)(4 * t);
+    }
     constexpr int RC = NT * 8;
-    float acc[NT][4];
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+    constexpr int UNR = NT <= 2 ? 4 : 2;
     const int ksteps = kc * 4;
-    for (int item = 0; item < total_items; ++item) {
-        const int s = item % nstages;
-        const uint32_t ph = (uint32_t)(item / nstages) & 1u;
-        if (!mbar_wait(full_bar(s), ph, abort_flag, status)) return;
-        if (item == 0) GV_TRACE(4);
-        if (item == nstages) GV_TRACE(5);
-        const int grp = item / nchunks, chunk = item - grp * nchunks;
-        const uint32_t stage = ring_s + (uint32_t)(s * stage_bytes);
-        for (int ks = kphase; ks < ksteps; ks += kstride) {
-            const int c = ks >> 2, ks4 = ks & 3;
-            const int rowidx = c * group_rows + a_row;
-            uint32_t a[4];
-            ldmatrix_x4(a, stage + (uint32_t)(rowidx * 128) + (uint32_t)((((ks4 * 2 + a_chunk) ^ rowidx) & 7) << 4));
-            const int k = (chunk * kc + c) * 64 + ks4 * 16 + (lane & 15);
-            const uint32_t boff = (uint32_t)(hx_pos(k) * 16);
+    for (int grp = 0; grp < ngroups; ++grp) {
+        float acc[2][NT][4];
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                uint32_t b[2];
-                ldmatrix_x2_trans(b, hx_s + (uint32_t)((nt << logn) * 16) + boff);
-                mma16816_bf16_acc(acc[nt], a[0], a[1], a[2], a[3], b[0], b[1]);
-            }
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(empty_bar(s));
-        // refill the stage consumed one iteration ago: by now every warp has released it
-        if (item >= 1 && item - 1 + nstages < total_items) {
-            const int prev = item - 1;
-            if (!mbar_wait(empty_bar(prev % nstages), (uint32_t)(prev / nstages) & 1u, abort_flag, status)) return;
-            issue(prev + nstages);
-        }
-        if (chunk == nchunks - 1) {
-            // row group finished: reduce the warps' partial sums through shared memory
+        for (int h = 0; h < 2; ++h)
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                float *p = red + ((size_t)warp * 16 + g) * RC + nt * 8 + 2 * t;
-                p[0] = acc[nt][0];
-                p[1] = acc[nt][1];
-                p[8 * RC] = acc[nt][2];
-                p[8 * RC + 1] = acc[nt][3];
-                acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+            for (int nt = 0; nt < NT; ++nt) acc[h][nt][0] = acc[h][nt][1] = acc[h][nt][2] = acc[h][nt][3] = 0.f;
+        // Items are dealt to the warp groups by item number, and the number of stages is a multiple of the number
+        // of groups: a stage is always consumed by the same group, so its warps see every phase of its barrier
+        // (a one-bit phase parity cannot tell "not yet filled" from "filled twice since").
+        const int first = grp * nchunks;
+        for (int item = first + ((wg - first) & (GV_GROUPS - 1)); item < first + nchunks; item += GV_GROUPS) {
+            const int chunk = item - first;
+            const int s = item % nstages;
+            const uint32_t ph = (uint32_t)(item / nstages) & 1u;
+            if (!mbar_wait(full_bar(s), ph, abort_flag, status)) return;
+            if (item == 0) GV_TRACE(4);
+            const uint32_t stage = ring_s + (uint32_t)(s * stage_bytes);
+            // this warp's k steps of the item, UNR at a time: all fragment loads first, then the products
+            for (int ks0 = wj; ks0 < ksteps; ks0 += GV_GW * UNR) {
+                uint32_t a[UNR][2][4], b[UNR][NT][2];
+#pragma unroll
+                for (int u = 0; u < UNR; ++u) {
+                    const int ks = ks0 + u * GV_GW;
+                    if (ks < ksteps) {
+                        const int c = ks >> 2, ks4 = ks & 3;
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            if (h < rt) {
+                                const int rowidx = c * group_rows + h * 16 + a_row;
+                                ldmatrix_x4(a[u][h], stage + (uint32_t)(rowidx * 128) +
+                                                         (uint32_t)((((ks4 * 2 + a_chunk) ^ rowidx) & 7) << 4));
+                            }
+                        }
+                        const uint32_t koff = (uint32_t)(((chunk * kc + c) * 64 + ks4 * 16) * 2);
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt) {
+                            b[u][nt][0] = b_ok[nt] ? lds32(b_addr[nt] + koff) : 0u;
+                            b[u][nt][1] = b_ok[nt] ? lds32(b_addr[nt] + koff + 16) : 0u;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < UNR; ++u) {
+                    if (ks0 + u * GV_GW < ksteps) {
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            if (h < rt) {
+#pragma unroll
+                                for (int nt = 0; nt < NT; ++nt)
+                                    mma16816_bf16_acc(acc[h][nt], a[u][h][0], a[u][h][1], a[u][h][2], a[u][h][3],
+                                                      b[u][nt][0], b[u][nt][1]);
+                            }
+                        }
+                    }
+                }
             }
-            __syncthreads();
-            const int grp_row0 = row_begin + grp * group_rows;
-            for (int idx = tid; idx < rt * 16 * Bg; idx += GV_THREADS) {
-                const int r = idx / Bg, c = idx - r * Bg;   // r: row within the group
-                const int tile = r >> 4, rin = r & 15;
-                float sum = 0.f;
-                for (int w = tile; w < GV_WARPS; w += rt) sum += red[((size_t)w * 16 + rin) * RC + c];
-                const int row = grp_row0 + r;
-                if (r < group_rows && row < row_end) store_out(Y, (size_t)row * B + b0 + c, sum, out_dtype);
+            // Release the stage.  The warp of the group that is last to do so refills it at once: no warp waits
+            // for another here.  (The fence orders this warp's reads of the stage before the counter update.)
+            __syncwarp();
+            if (lane == 0) {
+                __threadfence_block();
+                const int done = atomicAdd(&released[s], 1);   // counts up over all uses of the stage
+                if ((done & (GV_GW - 1)) == GV_GW - 1 && item + nstages < total_items) issue(item + nstages);
             }
-            __syncthreads();
         }
+        // row group finished: reduce the 16 warps' partial sums through shared memory, upper half first
+        const int grp_row0 = row_begin + grp * group_rows;
+        float *mine = red + (size_t)(warp & 7) * 32 * RC;
+        if (warp >= 8) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    float *p = mine + (h * 16 + g) * RC + nt * 8 + 2 * t;
+                    p[0] = acc[h][nt][0];
+                    p[1] = acc[h][nt][1];
+                    p[8 * RC] = acc[h][nt][2];
+                    p[8 * RC + 1] = acc[h][nt][3];
+                }
+        }
+        __syncthreads();
+        if (warp < 8) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    float *p = mine + (h * 16 + g) * RC + nt * 8 + 2 * t;
+                    p[0] += acc[h][nt][0];
+                    p[1] += acc[h][nt][1];
+                    p[8 * RC] += acc[h][nt][2];
+                    p[8 * RC + 1] += acc[h][nt][3];
+                }
+        }
+        __syncthreads();
+        for (int idx = tid; idx < rt * 16 * Bg; idx += GV_THREADS) {
+            const int r = idx / Bg, c = idx - r * Bg;   // r: row within the group
+            float sum = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) sum += red[((size_t)w * 32 + r) * RC + c];
+            const int row = grp_row0 + r;
+            if (r < group_rows && row < row_end) store_out(Y, (size_t)row * B + b0 + c, sum, out_dtype);
+        }
+        __syncthreads();
     }
     GV_TRACE(6);
 }
@@ -507,19 +571,20 @@ static int launch_bf16_nt(const void *W, const void *X, void *Y, int M, int N, i
 }
 
 constexpr size_t kStreamSmemLimit = 225 * 1024;
-static size_t stream_fixed_smem(int N, int nt)
+static size_t stream_fixed_smem(int N, int cols)
 {
-    return (size_t)nt * N * 16 + (size_t)GV_WARPS * 16 * nt * 8 * 4 + 1024 /*alignment*/ + 16 * 16 + 64 /*barriers*/;
+    const int nt = (cols + 7) / 8;
+    return (((size_t)cols * hxt_pitch(N) + 127) & ~(size_t)127) + (size_t)(GV_WARPS / 2) * 32 * nt * 8 * 4 +
+           1024 /*alignment*/ + 16 * 16 + 64 /*barriers, counters*/;
 }
-// Column blocks (of 8) per launch on the fast path, 0 if the shape does not take it
-// (the ring needs room for at least two stages of up to 32 KB).
-static int stream_nt_max(int N, int B)
+// Columns per launch on the fast path (all of B, or a multiple of 8), 0 if the shape does not take it
+// (the ring needs room for at least 64 KB).
+static int stream_cols_max(int N, int B)
 {
     if (N < 256 || N > 8192) return 0;
-    int nt = (B + 7) / 8;
-    if (nt > 4) nt = 4;
-    while (nt > 1 && stream_fixed_smem(N, nt) + 64 * 1024 > kStreamSmemLimit) --nt;
-    return stream_fixed_smem(N, nt) + 64 * 1024 <= kStreamSmemLimit ? nt : 0;
+    int cols = B < 32 ? B : 32;
+    while (cols > 8 && stream_fixed_smem(N, cols) + 64 * 1024 > kStreamSmemLimit) cols = (cols - 1) & ~7;
+    return stream_fixed_smem(N, cols) + 64 * 1024 <= kStreamSmemLimit ? cols : 0;
 }
 
 template <int NT>
@@ -533,14 +598,23 @@ static int launch_stream_nt(const void *W, const void *X, void *Y, int M, int N,
     grid = (M + rows_per_cta - 1) / rows_per_cta;
     const int groups = (rows_per_cta + GV_MAX_GROUP_ROWS - 1) / GV_MAX_GROUP_ROWS;
     const int group_rows = (rows_per_cta + groups - 1) / groups;
-    // one TMA op = group_rows x (64*kc) elements, about 16-32 KB; kc is a power of two dividing N/64
-    int kc = 1;
-    while (kc * 2 <= N / 64 && group_rows * 128 * kc * 2 <= 32 * 1024 && kc < 16) kc *= 2;
-    const int stage_bytes = ((group_rows * 128 * kc) + 1023) & ~1023;
-    int stages = (int)((kStreamSmemLimit - stream_fixed_smem(N, NT)) / stage_bytes);
-    if (stages > 16) stages = 16;
-    if (stages < 2) return B200HT_ERR_SIZE;
-    const size_t smem = stream_fixed_smem(N, NT) + (size_t)stages * stage_bytes;
+    // One TMA op = group_rows x (64*kc) elements, at most 32 KB, kc a power of two dividing N/64.  The number of
+    // stages is a multiple of the number of warp groups (see the kernel); among the candidates take the one that
+    // keeps most bytes in flight, preferring at least one item per warp group and then the larger op.
+    const size_t ring_room = kStreamSmemLimit - stream_fixed_smem(N, Bg);
+    int kc = 0, stages = 0, stage_bytes = 0;
+    size_t best = 0;
+    for (int cand = 16; cand >= 1; cand >>= 1) {
+        if ((N / 64) % cand || (size_t)group_rows * 128 * cand > 32 * 1024) continue;
+        const int sb = ((group_rows * 128 * cand) + 1023) & ~1023;
+        int st = (int)(ring_room / sb);
+        st = (st > 16 ? 16 : st) & ~(GV_GROUPS - 1);
+        if (st < GV_GROUPS) continue;
+        const size_t score = (size_t)st * sb + ((N / 64) / cand >= GV_GROUPS ? (size_t)1 << 30 : 0);
+        if (score > best) { best = score; kc = cand; stages = st; stage_bytes = sb; }
+    }
+    if (!kc) return B200HT_ERR_SIZE;
+    const size_t smem = stream_fixed_smem(N, Bg) + (size_t)stages * stage_bytes;
     CUtensorMap tw;
     int rc = encode_tmap_bf16_rows_chunks(&tw, W, (uint64_t)M, (uint64_t)N, (uint32_t)group_rows, (uint32_t)kc);
     if (rc) return rc;
@@ -596,10 +670,10 @@ int launch_gemv(const void *W, const void *X, void *Y, int M, int N, int B, int 
         }
         return 0;
     }
-    // bf16 fast path: up to 4 blocks of 8 columns per launch
-    if (const int nt_max = stream_nt_max(N, B)) {
-        for (int b0 = 0; b0 < B; b0 += nt_max * 8) {
-            const int Bg = (B - b0) < nt_max * 8 ? (B - b0) : nt_max * 8;
+    // bf16 fast path: up to 32 columns per launch
+    if (const int cols_max = stream_cols_max(N, B)) {
+        for (int b0 = 0; b0 < B; b0 += cols_max) {
+            const int Bg = (B - b0) < cols_max ? (B - b0) : cols_max;
             const int rc = launch_stream(W, X, Y, M, N, logn, B, b0, Bg, out_dtype, scale, st);
             if (rc) return rc;
         }

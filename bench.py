@@ -21,6 +21,7 @@ no collective on the data path), so total work is fixed: strong scaling.
             2^15, HBM GB/s against the measured copy bandwidth
   gemv      secondary block: fused GEMV, W 4096 x 4096 bf16, B = 1, 4, 16, GB/s
   c3        secondary block: fused W.H(X) at K=1024, 4096 tokens, M=4096, fp32 and bf16
+  k4096     secondary block: fused W.H(X) at K=4096, M=16384, 16384 tokens, bf16, TFLOP/s
   cpu_baseline  the reference's torch path (explicit Hadamard matmul, then
             matmul; bench/bench.py:44-59 of the reference) on the host cores,
             on a bounded slice of the same tokens
@@ -274,6 +275,40 @@ def time_c3(pkg, torch, peaks, reps=10):
     return out
 
 
+def time_k4096(pkg, torch, peaks, reps=5):
+    """Fused W.H(X) at Hadamard size 4096 (bf16 in, fp32 accumulate, bf16 token-major out): M=16384, 16384 tokens.
+    W (134 MB) plus the tokens (134 MB) and the output (537 MB) exceed L2."""
+    K, N, M = 4096, 16384, 16384
+    g = torch.Generator(device="cuda").manual_seed(5)
+    X = torch.randn(N, K, generator=g, device="cuda").bfloat16()
+    W = (torch.randn(M, K, generator=g, device="cuda") / math.sqrt(K)).bfloat16()
+    C = torch.empty(N, M, dtype=torch.bfloat16, device="cuda")
+    ws = torch.empty(pkg.fused_gemm_workspace_bytes(M, N, K, torch.bfloat16), dtype=torch.uint8, device="cuda")
+    lib = pkg._lib.load()
+    st = torch.cuda.current_stream().cuda_stream
+
+    def call():
+        rc = lib.b200ht_fused_gemm(X.data_ptr(), W.data_ptr(), C.data_ptr(), M, N, K, pkg._lib.BF16, pkg._lib.BF16,
+                                   pkg._lib.OUT_NM, float(K ** -0.5), ws.data_ptr(), ws.numel(), st)
+        if rc:
+            raise RuntimeError(pkg._lib.error_string(rc))
+
+    for _ in range(3):
+        call()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        call()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    tf = 2.0 * M * N * K / (ms * 1e-3) / 1e12
+    return {"shape": {"K": K, "M": M, "tokens": N}, "ms": ms, "tflops": tf,
+            "frac_of_sustained": tf / peaks["bf16_tflops_sustained"], "frac_of_burst": tf / peaks["bf16_tflops"],
+            "frac_of_nominal_2250": tf / 2250.0}
+
+
 def run_gpu_arm(args):
     import torch
     import torch.distributed as dist
@@ -360,6 +395,7 @@ def run_gpu_arm(args):
     fwht = time_fwht_sweep(pkg, torch, peaks)
     gemv = time_gemv(pkg, torch, peaks)
     c3 = time_c3(pkg, torch, peaks)
+    k4096 = time_k4096(pkg, torch, peaks)
     if world > 1:
         agg = torch.tensor([fwht[k]["gbs"] for k in sorted(fwht, key=int)], device="cuda")
         dist.all_reduce(agg, op=dist.ReduceOp.SUM)
@@ -406,6 +442,7 @@ def run_gpu_arm(args):
             "fwht": fwht,
             "gemv": gemv,
             "c3": c3,
+            "k4096": k4096,
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": X.numel() * 2 * world, "d2h_bytes_per_step": C.numel() * 2 * world},
