@@ -275,7 +275,7 @@ template <int NT>
 __global__ void __launch_bounds__(GV_THREADS, 1)
 gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bfloat16 *X, void *Y, int M, int N,
                         int logn, int B, int b0, int Bg, int out_dtype, float scale, int rows_per_cta,
-                        int group_rows, int kc, int stage_bytes, int nstages, int *status)
+                        int group_rows, int kc, int stage_bytes, int nstages, int red_in_ring, int *status)
 {
     extern __shared__ unsigned char smem_dyn[];
     // ring first (1024-byte aligned stages for the 128-byte swizzle), then H(X), reduction buffer, barriers
@@ -283,8 +283,11 @@ gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bflo
     unsigned char *gen = smem_dyn + (ring_s - smem_u32(smem_dyn));
     const int pitch = hxt_pitch(N);
     unsigned char *hxT = gen + (size_t)nstages * stage_bytes;                     // [Bg][pitch]
-    float *red = (float *)(hxT + (((size_t)Bg * pitch + 127) & ~(size_t)127));    // [8 warps][32 rows][NT*8]
-    unsigned char *bar_mem = (unsigned char *)(red + (GV_WARPS / 2) * 32 * NT * 8);  // full[], counters, abort flag
+    // reduction buffer [8 warps][32 rows][NT*8]: its own space, or (red_in_ring, one row group per CTA only) the
+    // start of the ring, which is idle by the time the single reduction runs
+    unsigned char *after_hx = hxT + (((size_t)Bg * pitch + 127) & ~(size_t)127);
+    float *red = red_in_ring ? (float *)gen : (float *)after_hx;
+    unsigned char *bar_mem = after_hx + (red_in_ring ? 0 : (GV_WARPS / 2) * 32 * NT * 8 * 4);  // full[], counters, abort
     const uint32_t bar_s = smem_u32(bar_mem);
     int *released = (int *)(bar_mem + 8 * nstages);                               // warps done with stage s
     volatile int *abort_flag = (volatile int *)(bar_mem + 16 * nstages);
@@ -311,8 +314,15 @@ gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bflo
         tma_prefetch_desc(&tmW);
     }
     __syncthreads();
-    // programmatic dependent launch: barrier set-up above overlaps the predecessor's tail
+    // Programmatic dependent launch: the barrier set-up above overlaps the predecessor's tail, and so does a
+    // prefetch of X into L2 (a hint that returns no data, so it may run before the predecessor's writes are
+    // visible; it warms the address translation for the loads below).
     pdl_launch_dependents();
+    {
+        const size_t xbytes = (size_t)N * B * 2;
+        for (size_t off = (size_t)tid * 128; off < xbytes; off += (size_t)GV_THREADS * 128)
+            asm volatile("prefetch.global.L2 [%0];\n" ::"l"((const unsigned char *)X + off));
+    }
     pdl_wait();
 
     // one TMA op per ring item: group_rows x (64*kc) elements of W (issued by one thread)
@@ -323,38 +333,125 @@ gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bflo
         tma_load_3d(ring_s + (uint32_t)(s * stage_bytes), &tmW, 0, row_begin + grp * group_rows, chunk * kc,
                     full_bar(s));
     };
-    if (tid == 0) {
-        const int prologue = total_items < nstages ? total_items : nstages;
-        for (int item = 0; item < prologue; ++item) issue(item);
-    }
+    if (warp == 0 && lane < (total_items < nstages ? total_items : nstages)) issue(lane);   // nstages <= 16
     GV_TRACE(1);
 
     // ------------------------------ X^T into shared memory ------------------------------
+    // Every path issues all loads of a batch before the first store: a round trip to memory is long while the
+    // ring is filling, so the copy should cost one of them.
     if (B == 1) {
         const uint4 *Xv = (const uint4 *)X;
-        for (int v = tid; v < N / 8; v += GV_THREADS) ((uint4 *)hxT)[v] = __ldg(Xv + v);
+        for (int base = 0; base < N / 8; base += GV_THREADS * 2) {
+            uint4 r[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int v = base + u * GV_THREADS + tid;
+                if (v < N / 8) r[u] = __ldg(Xv + v);
+            }
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int v = base + u * GV_THREADS + tid;
+                if (v < N / 8) ((uint4 *)hxT)[v] = r[u];
+            }
+        }
+    } else if (B == 2) {
+        // 16 bytes = rows k..k+3 of both columns
+        const uint4 *Xv = (const uint4 *)X;
+        for (int base = 0; base < N / 4; base += GV_THREADS * 4) {
+            uint4 r[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int v = base + u * GV_THREADS + tid;
+                if (v < N / 4) r[u] = __ldg(Xv + v);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int v = base + u * GV_THREADS + tid;
+                const uint4 x = r[u];
+                if (v < N / 4) {
+                    *(uint2 *)(hxT + v * 8) = make_uint2(__byte_perm(x.x, x.y, 0x5410), __byte_perm(x.z, x.w, 0x5410));
+                    *(uint2 *)(hxT + pitch + v * 8) =
+                        make_uint2(__byte_perm(x.x, x.y, 0x7632), __byte_perm(x.z, x.w, 0x7632));
+                }
+            }
+        }
+    } else if (B == 4) {
+        // 32 bytes = rows k..k+3 of the four columns
+        const uint4 *Xv = (const uint4 *)X;
+        for (int base = 0; base < N / 4; base += GV_THREADS * 4) {
+            uint4 rx[4], ry[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int v = base + u * GV_THREADS + tid;
+                if (v < N / 4) { rx[u] = __ldg(Xv + 2 * v); ry[u] = __ldg(Xv + 2 * v + 1); }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int v = base + u * GV_THREADS + tid;
+                const uint4 x = rx[u], y = ry[u];   // x: rows k, k+1; y: rows k+2, k+3
+                if (v < N / 4) {
+                    *(uint2 *)(hxT + v * 8) = make_uint2(__byte_perm(x.x, x.z, 0x5410), __byte_perm(y.x, y.z, 0x5410));
+                    *(uint2 *)(hxT + pitch + v * 8) =
+                        make_uint2(__byte_perm(x.x, x.z, 0x7632), __byte_perm(y.x, y.z, 0x7632));
+                    *(uint2 *)(hxT + 2 * pitch + v * 8) =
+                        make_uint2(__byte_perm(x.y, x.w, 0x5410), __byte_perm(y.y, y.w, 0x5410));
+                    *(uint2 *)(hxT + 3 * pitch + v * 8) =
+                        make_uint2(__byte_perm(x.y, x.w, 0x7632), __byte_perm(y.y, y.w, 0x7632));
+                }
+            }
+        }
     } else if ((B & 7) == 0 && (b0 & 7) == 0 && (Bg & 7) == 0) {
-        // two rows k, k+1 of one block of 8 columns per thread: two 16-byte loads, eight 4-byte stores
+        // two rows k, k+1 of one block of 8 columns per task: two 16-byte loads, eight 4-byte stores
         const uint4 *Xv = (const uint4 *)X;
         const int vpr = B >> 3, v0 = b0 >> 3, nb8 = Bg >> 3;
-        for (int idx = tid; idx < (N / 2) * nb8; idx += GV_THREADS) {
-            const int kp = idx / nb8, cb = idx - kp * nb8;
-            const uint4 x0 = __ldg(Xv + (size_t)(2 * kp) * vpr + v0 + cb);
-            const uint4 x1 = __ldg(Xv + (size_t)(2 * kp + 1) * vpr + v0 + cb);
-            const uint32_t w0[4] = {x0.x, x0.y, x0.z, x0.w}, w1[4] = {x1.x, x1.y, x1.z, x1.w};
-            unsigned char *dst = hxT + (size_t)(cb * 8) * pitch + kp * 4;
+        const int ntasks = (N / 2) * nb8;
+        for (int base = 0; base < ntasks; base += GV_THREADS * 8) {
+            uint4 r0[8], r1[8];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                *(uint32_t *)(dst + (size_t)(2 * j) * pitch) = __byte_perm(w0[j], w1[j], 0x5410);
-                *(uint32_t *)(dst + (size_t)(2 * j + 1) * pitch) = __byte_perm(w0[j], w1[j], 0x7632);
+            for (int u = 0; u < 8; ++u) {
+                const int idx = base + u * GV_THREADS + tid;
+                const int kp = idx / nb8, cb = idx - kp * nb8;
+                if (idx < ntasks) {
+                    r0[u] = __ldg(Xv + (size_t)(2 * kp) * vpr + v0 + cb);
+                    r1[u] = __ldg(Xv + (size_t)(2 * kp + 1) * vpr + v0 + cb);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int idx = base + u * GV_THREADS + tid;
+                const int kp = idx / nb8, cb = idx - kp * nb8;
+                if (idx < ntasks) {
+                    const uint32_t w0[4] = {r0[u].x, r0[u].y, r0[u].z, r0[u].w};
+                    const uint32_t w1[4] = {r1[u].x, r1[u].y, r1[u].z, r1[u].w};
+                    unsigned char *dst = hxT + (size_t)(cb * 8) * pitch + kp * 4;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        *(uint32_t *)(dst + (size_t)(2 * j) * pitch) = __byte_perm(w0[j], w1[j], 0x5410);
+                        *(uint32_t *)(dst + (size_t)(2 * j + 1) * pitch) = __byte_perm(w0[j], w1[j], 0x7632);
+                    }
+                }
             }
         }
     } else {
         const unsigned short *Xs = (const unsigned short *)X;
-        for (int idx = tid; idx < (N / 2) * Bg; idx += GV_THREADS) {
-            const int kp = idx / Bg, c = idx - kp * Bg;
-            const uint32_t lo = __ldg(Xs + (size_t)(2 * kp) * B + b0 + c), hi = __ldg(Xs + (size_t)(2 * kp + 1) * B + b0 + c);
-            *(uint32_t *)(hxT + (size_t)c * pitch + kp * 4) = lo | (hi << 16);
+        const int ntasks = (N / 2) * Bg;
+        for (int base = 0; base < ntasks; base += GV_THREADS * 8) {
+            uint32_t lo[8], hi[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int idx = base + u * GV_THREADS + tid;
+                const int kp = idx / Bg, c = idx - kp * Bg;
+                if (idx < ntasks) {
+                    lo[u] = __ldg(Xs + (size_t)(2 * kp) * B + b0 + c);
+                    hi[u] = __ldg(Xs + (size_t)(2 * kp + 1) * B + b0 + c);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int idx = base + u * GV_THREADS + tid;
+                const int kp = idx / Bg, c = idx - kp * Bg;
+                if (idx < ntasks) *(uint32_t *)(hxT + (size_t)c * pitch + kp * 4) = lo[u] | (hi[u] << 16);
+            }
         }
     }
     __syncthreads();
@@ -464,6 +561,7 @@ gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bflo
         // row group finished: reduce the 16 warps' partial sums through shared memory, upper half first
         const int grp_row0 = row_begin + grp * group_rows;
         float *mine = red + (size_t)(warp & 7) * 32 * RC;
+        if (red_in_ring) __syncthreads();   // every warp is done with the ring before it is reused
         if (warp >= 8) {
 #pragma unroll
             for (int h = 0; h < 2; ++h)
@@ -571,11 +669,12 @@ static int launch_bf16_nt(const void *W, const void *X, void *Y, int M, int N, i
 }
 
 constexpr size_t kStreamSmemLimit = 225 * 1024;
-static size_t stream_fixed_smem(int N, int cols)
+static size_t stream_fixed_smem(int N, int cols, bool red_in_ring = false)
 {
     const int nt = (cols + 7) / 8;
-    return (((size_t)cols * hxt_pitch(N) + 127) & ~(size_t)127) + (size_t)(GV_WARPS / 2) * 32 * nt * 8 * 4 +
-           1024 /*alignment*/ + 16 * 16 + 64 /*barriers, counters*/;
+    return (((size_t)cols * hxt_pitch(N) + 127) & ~(size_t)127) +
+           (red_in_ring ? 0 : (size_t)(GV_WARPS / 2) * 32 * nt * 8 * 4) + 1024 /*alignment*/ + 16 * 16 +
+           64 /*barriers, counters*/;
 }
 // Columns per launch on the fast path (all of B, or a multiple of 8), 0 if the shape does not take it
 // (the ring needs room for at least 64 KB).
@@ -601,20 +700,30 @@ static int launch_stream_nt(const void *W, const void *X, void *Y, int M, int N,
     // One TMA op = group_rows x (64*kc) elements, at most 32 KB, kc a power of two dividing N/64.  The number of
     // stages is a multiple of the number of warp groups (see the kernel); among the candidates take the one that
     // keeps most bytes in flight, preferring at least one item per warp group and then the larger op.
-    const size_t ring_room = kStreamSmemLimit - stream_fixed_smem(N, Bg);
     int kc = 0, stages = 0, stage_bytes = 0;
-    size_t best = 0;
-    for (int cand = 16; cand >= 1; cand >>= 1) {
-        if ((N / 64) % cand || (size_t)group_rows * 128 * cand > 32 * 1024) continue;
-        const int sb = ((group_rows * 128 * cand) + 1023) & ~1023;
-        int st = (int)(ring_room / sb);
-        st = (st > 16 ? 16 : st) & ~(GV_GROUPS - 1);
-        if (st < GV_GROUPS) continue;
-        const size_t score = (size_t)st * sb + ((N / 64) / cand >= GV_GROUPS ? (size_t)1 << 30 : 0);
-        if (score > best) { best = score; kc = cand; stages = st; stage_bytes = sb; }
+    auto plan = [&](bool red_in_ring) {
+        const size_t ring_room = kStreamSmemLimit - stream_fixed_smem(N, Bg, red_in_ring);
+        size_t best = 0;
+        kc = 0;
+        for (int cand = 16; cand >= 1; cand >>= 1) {
+            if ((N / 64) % cand || (size_t)group_rows * 128 * cand > 32 * 1024) continue;
+            const int sb = ((group_rows * 128 * cand) + 1023) & ~1023;
+            int st = (int)(ring_room / sb);
+            st = (st > 16 ? 16 : st) & ~(GV_GROUPS - 1);
+            if (st < GV_GROUPS) continue;
+            const size_t score = (size_t)st * sb + ((N / 64) / cand >= GV_GROUPS ? (size_t)1 << 30 : 0);
+            if (score > best) { best = score; kc = cand; stages = st; stage_bytes = sb; }
+        }
+    };
+    // the reduction buffer reuses the start of the ring when it runs once, at the end, and fits there
+    bool red_in_ring = groups == 1;
+    plan(red_in_ring);
+    if (red_in_ring && (!kc || (size_t)stages * stage_bytes < (size_t)(GV_WARPS / 2) * 32 * NT * 8 * 4)) {
+        red_in_ring = false;
+        plan(false);
     }
     if (!kc) return B200HT_ERR_SIZE;
-    const size_t smem = stream_fixed_smem(N, Bg) + (size_t)stages * stage_bytes;
+    const size_t smem = stream_fixed_smem(N, Bg, red_in_ring) + (size_t)stages * stage_bytes;
     CUtensorMap tw;
     int rc = encode_tmap_bf16_rows_chunks(&tw, W, (uint64_t)M, (uint64_t)N, (uint32_t)group_rows, (uint32_t)kc);
     if (rc) return rc;
@@ -623,7 +732,7 @@ static int launch_stream_nt(const void *W, const void *X, void *Y, int M, int N,
     if (e != cudaSuccess) return (int)e;
     return launch_pdl(gemv_bf16_stream_kernel<NT>, dim3(grid), dim3(GV_THREADS), smem, st, tw,
                       (const __nv_bfloat16 *)X, Y, M, N, logn, B, b0, Bg, out_dtype, scale, rows_per_cta, group_rows, kc,
-                      stage_bytes, stages, status_word_ptr());
+                      stage_bytes, stages, red_in_ring ? 1 : 0, status_word_ptr());
 }
 
 static int launch_stream(const void *W, const void *X, void *Y, int M, int N, int logn, int B, int b0, int Bg,
