@@ -333,7 +333,13 @@ gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bflo
         tma_load_3d(ring_s + (uint32_t)(s * stage_bytes), &tmW, 0, row_begin + grp * group_rows, chunk * kc,
                     full_bar(s));
     };
-    if (warp == 0 && lane < (total_items < nstages ? total_items : nstages)) issue(lane);   // nstages <= 16
+    // The first stages of the ring are requested by 16 lanes at once -- but only after every warp has issued its
+    // first batch of X loads (below): requests of one SM are served in order, and X must not queue behind the
+    // ring's first fill.
+    auto start_stream = [&]() {
+        __syncthreads();
+        if (warp == 0 && lane < (total_items < nstages ? total_items : nstages)) issue(lane);   // nstages <= 16
+    };
     GV_TRACE(1);
 
     // ------------------------------ X^T into shared memory ------------------------------
@@ -348,6 +354,7 @@ gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bflo
                 const int v = base + u * GV_THREADS + tid;
                 if (v < N / 8) r[u] = __ldg(Xv + v);
             }
+            if (base == 0) start_stream();
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
                 const int v = base + u * GV_THREADS + tid;
@@ -364,6 +371,7 @@ gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bflo
                 const int v = base + u * GV_THREADS + tid;
                 if (v < N / 4) r[u] = __ldg(Xv + v);
             }
+            if (base == 0) start_stream();
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const int v = base + u * GV_THREADS + tid;
@@ -385,6 +393,7 @@ gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bflo
                 const int v = base + u * GV_THREADS + tid;
                 if (v < N / 4) { rx[u] = __ldg(Xv + 2 * v); ry[u] = __ldg(Xv + 2 * v + 1); }
             }
+            if (base == 0) start_stream();
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const int v = base + u * GV_THREADS + tid;
@@ -416,6 +425,7 @@ gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bflo
                     r1[u] = __ldg(Xv + (size_t)(2 * kp + 1) * vpr + v0 + cb);
                 }
             }
+            if (base == 0) start_stream();
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
                 const int idx = base + u * GV_THREADS + tid;
@@ -446,6 +456,7 @@ gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bflo
                     hi[u] = __ldg(Xs + (size_t)(2 * kp + 1) * B + b0 + c);
                 }
             }
+            if (base == 0) start_stream();
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
                 const int idx = base + u * GV_THREADS + tid;

@@ -212,3 +212,20 @@ def test_output_of_more_than_2_31_elements(pkg, dtype, out_dtype, layout):
         assert float(err) <= tol, float(err)
     del C, Cv
     torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("M,N,B", [(4096, 256, 2), (300, 1024, 8), (6000, 4096, 24), (1000, 8192, 8),
+                                   (4741, 512, 12), (77, 4096, 40), (4096, 2048, 5), (10000, 256, 1),
+                                   (9000, 4096, 16), (8, 8192, 4), (29, 1024, 32)])
+def test_bf16_gemv_streaming_path_shapes(pkg, oracle, M, N, B):
+    """The bf16 path for 256 <= N <= 8192: every copy-in variant of X (B = 1, 2, 4, multiples of 8, others),
+    1 to 4 column tiles, column splits (B > 32), one and several row groups per CTA, ragged last rows."""
+    g = torch.Generator().manual_seed(1000 + M + N + B)
+    W = (torch.randn(M, N, generator=g) / N ** 0.5).bfloat16()
+    X = torch.randn(N, B, generator=g).bfloat16()
+    ref = oracle.fused_gemv_ref(W.double().numpy(), X.double().numpy())
+    Y = pkg.fused_ht_gemv(W.cuda(), X.cuda())
+    assert pkg.device_status() == 0
+    _check(oracle, Y.cpu().numpy(), ref, BF16_TOL)
+    Yb = pkg.fused_ht_gemv(W.cuda(), X.cuda(), out_dtype=torch.bfloat16)
+    _check(oracle, Yb.float().cpu().numpy(), ref, BF16_TOL)
