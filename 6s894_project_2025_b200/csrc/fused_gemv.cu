@@ -831,7 +831,7 @@ extern "C" int b200ht_fused_gemv(const void *W, const void *X, void *Y, int M, i
     if (in_dtype != B200HT_F32 && in_dtype != B200HT_BF16) return B200HT_ERR_DTYPE;
     if (out_dtype != B200HT_F32 && out_dtype != B200HT_BF16) return B200HT_ERR_DTYPE;
     if (N < 2 || N > (1 << kMaxLogN) || !is_pow2((uint64_t)N)) return B200HT_ERR_SIZE;
-    if (M < 0 || B < 1 || B > 64) return B200HT_ERR_SIZE;
+    if (M < 0 || B < 1 || B > 65536) return B200HT_ERR_SIZE;
     if (in_dtype == B200HT_BF16 && N < 32) return B200HT_ERR_SIZE;
     if (M == 0) return 0;
     if (!W || !X || !Y) return B200HT_ERR_NULL;

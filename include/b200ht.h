@@ -141,11 +141,15 @@ int b200ht_fused_gemm_static(const void *X, const void *W, void *C, int M, int N
 /*
  * Small-batch fused Y = W . H(X):  Y[m*B + b] = sum_k W[m*N + k] * (scale * H_N x_b)[k]
  *   W  M x N row-major, X  N x B with b fastest (X[i*B + b]), Y  M x B, b fastest.
- * N must be a power of two, 2 <= N <= 32768 (>= 32 for BF16); 1 <= B <= 64.
+ * N must be a power of two, 2 <= N <= 32768 (>= 32 for BF16); 1 <= B <= 65536
+ * (the reference's own benchmark calls it with B up to 2048,
+ * fused_ht/fwht_gemv_fusion.cu:643-653).
  * in_dtype F32 | BF16 (W and X alike), out_dtype F32 | BF16.  For BF16 with
  * 256 <= N <= 8192 W is streamed from HBM once per group of up to 32 columns
  * (once for B <= 32 when N <= 2048, for B <= 16 at N = 4096, for B <= 8 at
- * N = 8192); other shapes use smaller column groups.
+ * N = 8192); other shapes use smaller column groups.  The entry is built for
+ * small B: with more than 64 columns b200ht_fused_gemm (tokens = columns of
+ * X) reads W once and is the faster call.
  * Argument order W, X, Y, M, N, B as in
  *   __global__ void fused_hadamard_gemv_kernel(const float* W, const float* X,
  *   float* Y, int M, int N, int B)   (fused_ht/fwht_gemv_fusion.cu:98-105; the

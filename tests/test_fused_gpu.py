@@ -229,3 +229,32 @@ def test_bf16_gemv_streaming_path_shapes(pkg, oracle, M, N, B):
     _check(oracle, Y.cpu().numpy(), ref, BF16_TOL)
     Yb = pkg.fused_ht_gemv(W.cuda(), X.cuda(), out_dtype=torch.bfloat16)
     _check(oracle, Yb.float().cpu().numpy(), ref, BF16_TOL)
+
+
+@pytest.mark.parametrize("M,N,B", [(256, 256, 512), (64, 128, 256), (128, 256, 512), (512, 512, 1024)])
+def test_gemv_with_the_reference_benchmark_batches(pkg, oracle, M, N, B):
+    """The reference's own benchmark calls its GEMV kernel with B up to 2048 (fwht_gemv_fusion.cu:643-653).  The
+    Python entry serves B > 64 through the fused GEMM; the C entry loops over column groups.  Both must agree
+    with the oracle (fp32, unscaled as there)."""
+    g = torch.Generator().manual_seed(5)
+    W = torch.rand(M, N, generator=g) * 2 - 1
+    X = torch.rand(N, B, generator=g) * 2 - 1
+    ref = oracle.fused_gemv_ref(W.double().numpy(), X.double().numpy(), scale=1.0)
+    Wd, Xd = W.cuda(), X.cuda()
+    Y = pkg.fused_ht_gemv(Wd, Xd, scale=1.0)
+    assert Y.shape == (M, B)
+    _check(oracle, Y.cpu().numpy(), ref, F32_TOL)
+    lib = pkg._lib.load()
+    Y2 = torch.empty(M, B, device="cuda")
+    rc = lib.b200ht_fused_gemv(Wd.data_ptr(), Xd.data_ptr(), Y2.data_ptr(), M, N, B, pkg._lib.F32, pkg._lib.F32, 1.0,
+                               torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    _check(oracle, Y2.cpu().numpy(), ref, F32_TOL)
+    # bf16: the streaming path in column groups of 32
+    Yb = torch.empty(M, B, device="cuda")
+    Wb, Xb = Wd.bfloat16(), Xd.bfloat16()
+    rc = lib.b200ht_fused_gemv(Wb.data_ptr(), Xb.data_ptr(), Yb.data_ptr(), M, N, B,
+                               pkg._lib.BF16, pkg._lib.F32, 1.0, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    refb = oracle.fused_gemv_ref(W.bfloat16().double().numpy(), X.bfloat16().double().numpy(), scale=1.0)
+    _check(oracle, Yb.cpu().numpy(), refb, BF16_TOL)

@@ -56,7 +56,7 @@ def test_c_abi_rejects_bad_arguments_before_touching_the_gpu(lib):
     assert l.b200ht_fused_gemm(p16, p16, p16, 4, 4, 8, lib.F32, lib.F32, 0, 1.0, None, 0, None) == -5
     assert l.b200ht_fused_gemm(p16, p16, p16, 0, 4, 8, lib.F32, lib.F32, 0, 1.0, None, 0, None) == 0
     assert l.b200ht_fused_gemv(p16, p16, p16, 4, 12, 1, lib.F32, lib.F32, 1.0, None) == -2
-    assert l.b200ht_fused_gemv(p16, p16, p16, 4, 16, 65, lib.F32, lib.F32, 1.0, None) == -2
+    assert l.b200ht_fused_gemv(p16, p16, p16, 4, 16, 65537, lib.F32, lib.F32, 1.0, None) == -2
     assert l.b200ht_fused_gemv(p16, p16, p16, 4, 16, 1, lib.F16, lib.F32, 1.0, None) == -3
     assert l.b200ht_fused_gemm_workspace_bytes(128, 32, 256, lib.F32) == 32 * 256 * 4
     assert l.b200ht_fused_gemm_workspace_bytes(128, 32, 256, lib.BF16) == 32 * 256 * 2
