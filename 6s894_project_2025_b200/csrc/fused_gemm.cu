@@ -143,7 +143,86 @@ static int launch_sgemm(const float *A, const float *Bm, void *C, int M, int N, 
     return (int)cudaGetLastError();
 }
 
+// ---------------------------------------------------------------------------
+// fp32 on the tensor cores: every fp32 operand is the exact sum of three bf16
+// terms (8 + 8 + 8 significant bits), a = a1 + a2 + a3.  Of the nine cross
+// products the six with weight >= 2^-16 are kept,
+//   a.b ~ a1.b3 + a3.b1 + a2.b2 + a1.b2 + a2.b1 + a1.b1      (dropped: ~3 * 2^-24 |a.b|),
+// every bf16 x bf16 product is exact in the fp32 accumulator, and the six
+// partial contractions are one bf16 GEMM over a K axis six times as long:
+// row m of W becomes [w1 w3 w2 w1 w2 w1] and token row n of H(X) becomes
+// [y3 y1 y2 y2 y1 y1] (six blocks of K), smallest terms first.  The contraction
+// then runs on the tcgen05 kernel at bf16 rate / 6 instead of the FFMA rate.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) split3_kernel(const float4 *src, __nv_bfloat16 *dst, size_t nvec, int K,
+                                                     int is_w)
+{
+    const int kv = K >> 2;   // float4 per row
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
+        const float4 v = src[i];
+        const size_t row = i / kv;
+        const int k = (int)(i - row * kv) * 4;
+        const float a[4] = {v.x, v.y, v.z, v.w};
+        uint2 t[3];
+        uint32_t h[3][4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float r = a[e];
+#pragma unroll
+            for (int j = 0; j < 3; ++j) {
+                const __nv_bfloat16 b = __float2bfloat16_rn(r);
+                h[j][e] = (uint32_t)__bfloat16_as_ushort(b);
+                r -= __bfloat162float(b);   // exact
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 3; ++j) t[j] = make_uint2(h[j][0] | (h[j][1] << 16), h[j][2] | (h[j][3] << 16));
+        __nv_bfloat16 *o = dst + row * (size_t)(6 * K) + k;
+        // block order (smallest products first): W: 1 3 2 1 2 1 ; H(X): 3 1 2 2 1 1
+        const int pw[6] = {0, 2, 1, 0, 1, 0}, py[6] = {2, 0, 1, 1, 0, 0};
+#pragma unroll
+        for (int b = 0; b < 6; ++b) *(uint2 *)(o + (size_t)b * K) = t[is_w ? pw[b] : py[b]];
+    }
+}
+
+static size_t fp32_tc_workspace_bytes(int M, int N, int K)
+{
+    const size_t a = (((size_t)N * K * 4) + 255) & ~(size_t)255;
+    const size_t b = (((size_t)M * K * 12) + 255) & ~(size_t)255;
+    const size_t c = (((size_t)N * K * 12) + 255) & ~(size_t)255;
+    return a + b + c;
+}
+// Shapes that take the split path: rows long enough for the tcgen05 kernel, enough work to hide the two extra
+// passes over the operands, and K <= 4096.  The tensor core adds into its fp32 accumulator with truncation, so the
+// error of a contraction grows with its length: measured relative error (Frobenius) 1.0e-6 at K = 1024, 4.4e-6 at
+// K = 4096, 9.1e-6 at K = 8192 (FFMA kernel: 0.6e-6, 1.2e-6, 1.6e-6); beyond 4096 the margin to 1e-5 is gone.
+static bool fp32_tc_shape(int M, int N, int K) { return K >= 32 && K <= 4096 && (double)M * N * K >= 5e8; }
+
+static int launch_fp32_tc(const float *W, const float *Y, void *C, int M, int N, int K, int out_dtype, int out_layout,
+                          unsigned char *ws, cudaStream_t st)
+{
+    __nv_bfloat16 *Ws = (__nv_bfloat16 *)ws;
+    __nv_bfloat16 *Ys = (__nv_bfloat16 *)(ws + ((((size_t)M * K * 12) + 255) & ~(size_t)255));
+    const size_t wv = (size_t)M * K / 4, yv = (size_t)N * K / 4;
+    const int cap = 148 * 16;
+    split3_kernel<<<(unsigned)((wv + 255) / 256 < (size_t)cap ? (wv + 255) / 256 : cap), 256, 0, st>>>(
+        (const float4 *)W, Ws, wv, K, 1);
+    split3_kernel<<<(unsigned)((yv + 255) / 256 < (size_t)cap ? (yv + 255) / 256 : cap), 256, 0, st>>>(
+        (const float4 *)Y, Ys, yv, K, 0);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    return launch_gemm_bf16_tcgen05(Ys, Ws, C, M, N, 6 * K, out_dtype, out_layout, st);
+}
+
 }  // namespace b200ht
+
+extern "C" size_t b200ht_fused_gemm_tc_workspace_bytes(int M, int N, int K, int in_dtype)
+{
+    using namespace b200ht;
+    if (N <= 0 || K <= 0 || M <= 0) return 0;
+    if (in_dtype != B200HT_F32 || !fp32_tc_shape(M, N, K)) return b200ht_fused_gemm_workspace_bytes(M, N, K, in_dtype);
+    return fp32_tc_workspace_bytes(M, N, K);
+}
 
 extern "C" size_t b200ht_fused_gemm_workspace_bytes(int M, int N, int K, int in_dtype)
 {
@@ -176,8 +255,14 @@ static int fused_gemm_entry(const void *X, const void *W, void *C, int M, int N,
     cudaStream_t st = (cudaStream_t)stream;
     rc = launch_fwht(X, workspace, (uint64_t)N, (uint32_t)K, in_dtype, scale, signs, st);
     if (rc) return rc;
-    if (in_dtype == B200HT_F32)
+    if (in_dtype == B200HT_F32) {
+        // a workspace of the larger size (b200ht_fused_gemm_tc_workspace_bytes) selects the split-bf16 tensor-core
+        // contraction, the minimal one the exact FFMA kernel
+        if (fp32_tc_shape(M, N, K) && workspace_bytes >= fp32_tc_workspace_bytes(M, N, K))
+            return launch_fp32_tc((const float *)W, (const float *)workspace, C, M, N, K, out_dtype, out_layout,
+                                  (unsigned char *)workspace + ((((size_t)N * K * 4) + 255) & ~(size_t)255), st);
         return launch_sgemm((const float *)W, (const float *)workspace, C, M, N, K, out_dtype, out_layout, st);
+    }
     return launch_gemm_bf16_tcgen05(workspace, W, C, M, N, K, out_dtype, out_layout, st);
 }
 
@@ -256,6 +341,5 @@ extern "C" int b200ht_fused_gemm_static(const void *X, const void *W, void *C, i
     // Same two phases as b200ht_fused_gemm, on the resolved device address.  Every row of the
     // scratch that the contraction reads is written by the transform phase of this same call,
     // so nothing has to be cleared between calls.
-    return b200ht_fused_gemm(X, W, C, M, N, K, in_dtype, out_dtype, out_layout, scale, scratch,
-                             (size_t)B200HT_STATIC_SCRATCH_BYTES, stream);
+    return b200ht_fused_gemm(X, W, C, M, N, K, in_dtype, out_dtype, out_layout, scale, scratch, need, stream);
 }

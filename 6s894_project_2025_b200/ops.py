@@ -91,14 +91,18 @@ def hadamard_transform(x: torch.Tensor, inplace: bool = False, *, scale: float |
     return out.view(x.shape)
 
 
-def fused_gemm_workspace_bytes(M: int, N: int, K: int, dtype: torch.dtype) -> int:
-    return int(_lib.load().b200ht_fused_gemm_workspace_bytes(M, N, K, _DT[dtype]))
+def fused_gemm_workspace_bytes(M: int, N: int, K: int, dtype: torch.dtype, exact: bool = False) -> int:
+    """Workspace size for ``fused_ht_gemm``.  For fp32 inputs the default size selects the tensor-core
+    contraction (three bf16 terms per operand), ``exact=True`` the size of the FFMA path."""
+    lib = _lib.load()
+    fn = lib.b200ht_fused_gemm_workspace_bytes if exact else lib.b200ht_fused_gemm_tc_workspace_bytes
+    return int(fn(M, N, K, _DT[dtype]))
 
 
 def fused_ht_gemm(X: torch.Tensor, W: torch.Tensor, *, scale: float | None = None,
                   out_dtype: torch.dtype | None = None, out_layout: str = "mn",
                   out: torch.Tensor | None = None, workspace: torch.Tensor | None = None,
-                  signs: torch.Tensor | None = None) -> torch.Tensor:
+                  signs: torch.Tensor | None = None, exact: bool = False) -> torch.Tensor:
     """C = W . H(X): ``C[m, t] = sum_k W[m, k] * (scale * H_K x_t)[k]``.
 
     ``X`` is (N tokens, K) token-major and ``W`` is (M, K) row-major, the
@@ -108,6 +112,11 @@ def fused_ht_gemm(X: torch.Tensor, W: torch.Tensor, *, scale: float | None = Non
     reference's (M, N) matrix, ``"nm"`` the token-major (N, M) one.  ``scale``
     defaults to 1/sqrt(K); the reference executable computes ``scale=1.0``.
     ``signs`` (K entries, negative = flip; bf16 inputs only) computes W . H(d * X).
+    fp32 inputs on large shapes with K <= 4096 are contracted on the tensor
+    cores as six bf16 products per fp32 product (relative error up to 4.4e-6
+    at K = 4096, about 4x faster than FFMA);
+    ``exact=True``, or a caller ``workspace`` of only the minimal size, keeps
+    the FFMA kernel.
     """
     if X.dtype != W.dtype or X.dtype not in (torch.float32, torch.bfloat16):
         raise RuntimeError("fused_ht_gemm: X and W must both be float32 or both bfloat16")
@@ -136,13 +145,14 @@ def fused_ht_gemm(X: torch.Tensor, W: torch.Tensor, *, scale: float | None = Non
         raise RuntimeError("fused_ht_gemm: out has the wrong shape, dtype or strides")
     need = int(lib.b200ht_fused_gemm_workspace_bytes(M, N, K, _DT[X.dtype]))
     if workspace is None:
-        workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=X.device)
+        want = need if exact else int(lib.b200ht_fused_gemm_tc_workspace_bytes(M, N, K, _DT[X.dtype]))
+        workspace = torch.empty(max(want, 256), dtype=torch.uint8, device=X.device)
     elif workspace.numel() * workspace.element_size() < need:
         raise RuntimeError("fused_ht_gemm: workspace too small")
     if M > 0 and N > 0:
         with torch.cuda.device(X.device):
             layout = _lib.OUT_MN if out_layout == "mn" else _lib.OUT_NM
-            wsb = workspace.numel() * workspace.element_size()
+            wsb = need if exact else workspace.numel() * workspace.element_size()
             if signs is None:
                 rc = lib.b200ht_fused_gemm(X.data_ptr(), W.data_ptr(), out.data_ptr(), M, N, K, _DT[X.dtype],
                                            _DT[out_dtype], layout, float(scale), workspace.data_ptr(), wsb,

@@ -258,3 +258,36 @@ def test_gemv_with_the_reference_benchmark_batches(pkg, oracle, M, N, B):
     assert rc == 0
     refb = oracle.fused_gemv_ref(W.bfloat16().double().numpy(), X.bfloat16().double().numpy(), scale=1.0)
     _check(oracle, Yb.cpu().numpy(), refb, BF16_TOL)
+
+
+@pytest.mark.parametrize("M,N,K", [(1024, 768, 1024), (600, 900, 4096), (4096, 4096, 32), (2000, 3000, 128)])
+def test_fp32_tensor_core_contraction(pkg, oracle, M, N, K):
+    """fp32 inputs on shapes large enough for the split-bf16 tensor-core contraction (three bf16 terms per operand,
+    six products): same 1e-5 bar as the FFMA kernel, both layouts and output types, and `exact=True` still gives
+    the FFMA result."""
+    lib = pkg._lib.load()
+    assert lib.b200ht_fused_gemm_tc_workspace_bytes(M, N, K, pkg._lib.F32) > \
+        lib.b200ht_fused_gemm_workspace_bytes(M, N, K, pkg._lib.F32)
+    inp = oracle.make_inputs("c3", K=K, N=N, M=M)
+    X, W = inp["X"], inp["W"]
+    ref = oracle.fused_gemm_ref(X.numpy(), W.numpy())
+    Xd, Wd = X.cuda(), W.cuda()
+    for layout in ("mn", "nm"):
+        C = pkg.fused_ht_gemm(Xd, Wd, out_layout=layout).cpu().numpy()
+        _check(oracle, C if layout == "mn" else C.T, ref, F32_TOL)
+    Ce = pkg.fused_ht_gemm(Xd, Wd, exact=True).cpu().numpy()
+    _check(oracle, Ce, ref, F32_TOL)
+    Cb = pkg.fused_ht_gemm(Xd, Wd, out_dtype=torch.bfloat16).float().cpu().numpy()
+    _check(oracle, Cb, ref, 1e-2)   # bf16 rounding of the result only
+    assert pkg.device_status() == 0
+
+
+def test_fp32_long_rows_keep_the_ffma_kernel(pkg):
+    # K = 8192: the tensor-core accumulator's truncation error would reach the 1e-5 bar, so the split path is off
+    lib = pkg._lib.load()
+    assert lib.b200ht_fused_gemm_tc_workspace_bytes(2048, 2048, 8192, pkg._lib.F32) == \
+        lib.b200ht_fused_gemm_workspace_bytes(2048, 2048, 8192, pkg._lib.F32)
+    assert lib.b200ht_fused_gemm_tc_workspace_bytes(64, 64, 64, pkg._lib.F32) == \
+        lib.b200ht_fused_gemm_workspace_bytes(64, 64, 64, pkg._lib.F32)
+    assert lib.b200ht_fused_gemm_tc_workspace_bytes(4096, 4096, 1024, pkg._lib.BF16) == \
+        lib.b200ht_fused_gemm_workspace_bytes(4096, 4096, 1024, pkg._lib.BF16)
