@@ -476,6 +476,13 @@ def run_profile_case(case: str):
         for _ in range(4):
             C = pkg.fused_ht_gemm(X, W, out_layout="nm", out_dtype=torch.bfloat16)
         print("gemm case done", float(C.float().abs().mean()))
+    elif case == "c3":      # fused W.H(X) at K=1024, 4096 tokens, M=4096, bf16 in, fp32 M x N out; rotating inputs
+        K, M, N = 1024, 4096, 4096
+        sets = [(torch.randn(N, K, generator=g, device="cuda").bfloat16(), torch.randn(M, K, generator=g, device="cuda").bfloat16())
+                for _ in range(4)]
+        for X, W in sets:
+            C = pkg.fused_ht_gemm(X, W)
+        print("c3 case done", float(C.abs().mean()))
     elif case == "fwht":    # standalone transform, n = 1024, 4096, 8192 and 32768 (bf16), 134-268 MB, distinct buffers
         for n, rows in ((1024, 65536), (4096, 16384), (8192, 16384), (32768, 4096)):
             bufs = [torch.randn(rows, n, generator=g, device="cuda").bfloat16() for _ in range(3)]
@@ -498,7 +505,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--profile-case", default=None, choices=["gemm", "gemm-full", "fwht", "gemv"],
+    ap.add_argument("--profile-case", default=None, choices=["gemm", "gemm-full", "fwht", "gemv", "c3"],
                     help="run a few launches of ONE kernel on a reduced shape and exit (for ncu captures)")
     args = ap.parse_args()
     if args.profile_case:
