@@ -436,8 +436,9 @@ def run_gpu_arm(args):
                        "out": "bf16 token-major"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak,
-                         # DRAM bytes of one full-size GEMM launch on one GPU, from the committed ncu capture
-                         # (profiles/gemm_tc_kernel_fused_k8192.md); scaled by the token share of a rank
+                         # DRAM read + write bytes of one full-size GEMM launch on one GPU, from a one-pass ncu capture
+                         # of `bench.py --profile-case gemm-full` (dram__bytes_read.sum + dram__bytes_write.sum);
+                         # scaled by the token share of a rank
                          "traffic": 6.906e9 * n_local / N_TOKENS, "traffic_unit": "B/launch",
                          "peak_source": f"{peaks['source']} sustained cuBLAS bf16 (burst {peaks['bf16_tflops']})",
                          "frac_of_burst": achieved / peaks["bf16_tflops"]},

@@ -64,7 +64,9 @@ def load_reference_bench(ref_root: Path):
 
 
 def main() -> None:
-    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <checkout of Alan-Chen99/6s894_project_2025>")
+    ref_root = Path(sys.argv[1])
     out_dir = Path(__file__).resolve().parent
     bench = load_reference_bench(ref_root)
 
