@@ -113,7 +113,7 @@ __global__ void __launch_bounds__(256) fwht_reg_kernel(const uint4 *in, uint4 *o
 }
 
 // ---------------------------------------------------------------------------
-// n = 8192, 16384 (and 32768 for unaligned buffers), 16-bit: a CTA of 8 warps holds a slab of SLAB_ROWS rows in
+// n = 8192, 16384 (and 32768 for unaligned buffers), 16-bit: a CTA of 4 or 8 warps holds a slab of SLAB_ROWS rows in
 // shared memory.  Chunk c (256 elements = 32 vectors) sits at vector offset 33*c
 // so that both the contiguous accesses of pass 1 and the chunk-strided accesses
 // of pass 2 are bank-conflict free.
@@ -129,14 +129,15 @@ struct SmemCfg {
     static constexpr int CPR = 1 << Q;
     static constexpr int NCHUNK = SLAB_ROWS * CPR;
     static constexpr int SMEM_BYTES = NCHUNK * 33 * 16;
+    static constexpr int NW = LOGN == 13 ? 4 : 8;   // warps per CTA (measured: 4 is 2 % faster at n = 8192, 11 % slower at 16384)
 };
 
 template <int DT, int LOGN, bool SG>
-__global__ void __launch_bounds__(256) fwht_smem_kernel(const uint4 *in, uint4 *out, uint64_t rows,
+__global__ void __launch_bounds__(SmemCfg<LOGN>::NW * 32) fwht_smem_kernel(const uint4 *in, uint4 *out, uint64_t rows,
                                                         float mult, const uint4 *signs)
 {
     using Cfg = SmemCfg<LOGN>;
-    constexpr int Q = Cfg::Q, CPR = Cfg::CPR;
+    constexpr int Q = Cfg::Q, CPR = Cfg::CPR, NW = Cfg::NW;
     extern __shared__ uint4 sm[];
     pdl_launch_dependents();
     pdl_wait();
@@ -153,23 +154,23 @@ __global__ void __launch_bounds__(256) fwht_smem_kernel(const uint4 *in, uint4 *
     make_hfrag<DT>(A1, lane, 15u, 0.25f);
     make_hfrag<DT>(A2, lane, 15u, 0.25f);
 
-    constexpr int U = 4;
-    for (int c0 = warp; c0 < chunks_here; c0 += 8 * U) {
+    constexpr int U = 8;   // chunks (16-byte loads per lane) in flight per warp: 8 is 3-5 % faster than 4
+    for (int c0 = warp; c0 < chunks_here; c0 += NW * U) {
         uint4 v[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const int c = c0 + 8 * u;
+            const int c = c0 + NW * u;
             v[u] = c < chunks_here ? ld_stream(gin + c * 32 + lane) : make_uint4(0, 0, 0, 0);
         }
         if constexpr (SG) {
 #pragma unroll
-            for (int u = 0; u < U; ++u) flip_signs(v[u], signs, (uint32_t)(((c0 + 8 * u) & (CPR - 1)) * 32 + lane));
+            for (int u = 0; u < U; ++u) flip_signs(v[u], signs, (uint32_t)(((c0 + NW * u) & (CPR - 1)) * 32 + lane));
         }
         float o[U][8];
         rot8x<DT, U>(v, o, A1, A2);
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const int c = c0 + 8 * u;
+            const int c = c0 + NW * u;
             if (c < chunks_here) {
                 uint4 r;
                 r.x = pack2<DT>(o[u][0], o[u][1]);
@@ -188,7 +189,11 @@ __global__ void __launch_bounds__(256) fwht_smem_kernel(const uint4 *in, uint4 *
     make_hfrag<DT>(A2, lane, M2, 0.5f);
     constexpr int J = Q > 5 ? (1 << (Q - 5)) : 1;
     const int nitems = Q >= 5 ? rows_here * 32 : rows_here * 16;
-    for (int item = warp; item < nitems; item += 8) {
+    // Q == 5 (n = 8192, one row per CTA, 4 warps): a warp takes SPW = 8 consecutive slots, so that it alone writes, and afterwards reads,
+    // SPW*16 contiguous bytes of every chunk and no CTA-wide barrier is needed before the copy-out
+    constexpr int SPW = 32 / NW;
+    for (int it = 0; it < (Q == 5 ? SPW : (nitems - warp + NW - 1) / NW); ++it) {
+        const int item = Q == 5 ? warp * SPW + it : warp + it * NW;
         int slot, chunk0;
         if constexpr (Q >= 5) {
             slot = item & 31;
@@ -226,16 +231,36 @@ __global__ void __launch_bounds__(256) fwht_smem_kernel(const uint4 *in, uint4 *
             sm[(chunk0 + 32 * j) * 33 + slot] = r;
         }
     }
-    __syncthreads();
-
-    for (int c = warp; c < chunks_here; c += 8) st_stream(gout + c * 32 + lane, sm[c * 33 + lane]);
+    if constexpr (Q == 5) {
+        __syncwarp();
+        // pass 3, warp-local: 32/SPW chunks x SPW slots per instruction, four instructions in flight
+        constexpr int CPI = 32 / SPW;
+        const int sub = lane % SPW, cl = lane / SPW;
+        const int v0 = warp * SPW + sub;
+        for (int c0 = 0; c0 < chunks_here; c0 += 4 * CPI) {
+            uint4 r[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int c = c0 + u * CPI + cl;
+                if (c < chunks_here) r[u] = sm[c * 33 + v0];
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int c = c0 + u * CPI + cl;
+                if (c < chunks_here) st_stream(gout + c * 32 + v0, r[u]);
+            }
+        }
+    } else {
+        __syncthreads();
+        for (int c = warp; c < chunks_here; c += NW) st_stream(gout + c * 32 + lane, sm[c * 33 + lane]);
+    }
 }
 
 // ---------------------------------------------------------------------------
-// n = 4096 (written for 4096 .. 32768), 16-bit, second variant: a CTA of 8 warps
+// n = 4096 (written for 4096 .. 32768), 16-bit, second variant: a CTA of 4 warps
 // holds a 32 KB slab of rows in shared memory, chunk c (256 elements = 32 vectors)
 // at vector offset 32c.
-//   pass 1: a warp takes 4 consecutive chunks: index bits 0..7 through rot8 (the
+//   pass 1: a warp takes 4 consecutive chunks (two such groups at a time): index bits 0..7 through rot8 (the
 //           only tensor-core work: 4 mma.sync per 256 elements, as for n <= 2048),
 //           bits 8, 9 as fp32 butterflies across the 4 chunks, result rounded to
 //           16 bit into shared memory
@@ -252,6 +277,9 @@ __global__ void __launch_bounds__(256) fwht_smem_kernel(const uint4 *in, uint4 *
 // ---------------------------------------------------------------------------
 template <int LOGN>
 struct Smem2Cfg {
+    static constexpr int NW = 4;    // warps per CTA
+    static constexpr int G = 2;     // groups of 4 chunks a warp loads at once (8 x 16 bytes in flight per lane);
+                                    // measured at n = 4096: (NW, G) = (4, 2) 6.0 TB/s, (8, 1) 5.8, (4, 1) 5.4
     static constexpr int SLAB_ELEMS = LOGN >= 15 ? (1 << 15) : (1 << 14);
     static constexpr int SLAB_ROWS = SLAB_ELEMS >> LOGN;
     static constexpr int CPR = 1 << (LOGN - 8);             // chunks per row
@@ -263,7 +291,7 @@ struct Smem2Cfg {
 };
 
 template <int DT, int LOGN, bool SG>
-__global__ void __launch_bounds__(256) fwht_smem2_kernel(const uint4 *in, uint4 *out, uint64_t rows,
+__global__ void __launch_bounds__(Smem2Cfg<LOGN>::NW * 32) fwht_smem2_kernel(const uint4 *in, uint4 *out, uint64_t rows,
                                                          float mult, const uint4 *signs)
 {
     using Cfg = Smem2Cfg<LOGN>;
@@ -285,38 +313,46 @@ __global__ void __launch_bounds__(256) fwht_smem2_kernel(const uint4 *in, uint4 
         uint32_t A1[4], A2[4];
         make_hfrag<DT>(A1, lane, 15u, 0.25f);
         make_hfrag<DT>(A2, lane, 15u, 0.25f);
-        for (int g0 = warp * 4; g0 < chunks_here; g0 += 8 * 4) {
-            uint4 v[4];
+        constexpr int G = Cfg::G, NW = Cfg::NW;   // a warp takes G groups of 4 chunks at once: 4*G loads in flight per lane
+        for (int g0 = warp * 4 * G; g0 < chunks_here; g0 += NW * 4 * G) {
+            uint4 v[4 * G];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) v[u] = ld_stream(gin + (g0 + u) * 32 + lane);
+            for (int u = 0; u < 4 * G; ++u)
+                v[u] = g0 + u < chunks_here ? ld_stream(gin + (g0 + u) * 32 + lane) : make_uint4(0, 0, 0, 0);
             if constexpr (SG) {
 #pragma unroll
-                for (int u = 0; u < 4; ++u) flip_signs(v[u], signs, (uint32_t)(((g0 + u) & (CPR - 1)) * 32 + lane));
+                for (int u = 0; u < 4 * G; ++u)
+                    if (g0 + u < chunks_here) flip_signs(v[u], signs, (uint32_t)(((g0 + u) & (CPR - 1)) * 32 + lane));
             }
-            float o[4][8];
-            rot8x<DT, 4>(v, o, A1, A2);
+            float o[4 * G][8];
+            rot8x<DT, 4 * G>(v, o, A1, A2);
 #pragma unroll
-            for (int s = 1; s < 4; s <<= 1) {
+            for (int gg = 0; gg < G; ++gg) {
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    if (!(u & s)) {
+                for (int s = 1; s < 4; s <<= 1) {
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) {
-                            const float x = o[u][e], y = o[u | s][e];
-                            o[u][e] = x + y;
-                            o[u | s][e] = x - y;
+                    for (int u = 0; u < 4; ++u) {
+                        if (!(u & s)) {
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) {
+                                const float x = o[gg * 4 + u][e], y = o[gg * 4 + (u | s)][e];
+                                o[gg * 4 + u][e] = x + y;
+                                o[gg * 4 + (u | s)][e] = x - y;
+                            }
                         }
                     }
                 }
             }
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                uint4 r;
-                r.x = pack2<DT>(o[u][0], o[u][1]);
-                r.y = pack2<DT>(o[u][2], o[u][3]);
-                r.z = pack2<DT>(o[u][4], o[u][5]);
-                r.w = pack2<DT>(o[u][6], o[u][7]);
-                sm[(g0 + u) * 32 + lane] = r;
+            for (int u = 0; u < 4 * G; ++u) {
+                if (g0 + u < chunks_here) {
+                    uint4 r;
+                    r.x = pack2<DT>(o[u][0], o[u][1]);
+                    r.y = pack2<DT>(o[u][2], o[u][3]);
+                    r.z = pack2<DT>(o[u][4], o[u][5]);
+                    r.w = pack2<DT>(o[u][6], o[u][7]);
+                    sm[(g0 + u) * 32 + lane] = r;
+                }
             }
         }
     }
@@ -326,7 +362,7 @@ __global__ void __launch_bounds__(256) fwht_smem2_kernel(const uint4 *in, uint4 
     constexpr int SLOTS = 32 >> SB;                // consecutive vectors handled by the low lane bits
     const int lane_lo = lane & (SLOTS - 1), lane_hi = lane >> (5 - SB);
     const int ntasks = rows_here * 4 * (1 << SB);  // (row, chunk low 2 bits, slot block)
-    for (int task = warp; task < ntasks; task += 8) {
+    for (int task = warp; task < ntasks; task += Cfg::NW) {
         const int sblk = task & ((1 << SB) - 1);
         const int clow = (task >> SB) & 3;
         const int row = task >> (SB + 2);
@@ -454,8 +490,8 @@ static int launch_smem(const void *in, void *out, uint64_t rows, float scale, co
     auto go = [&](auto kernel) -> int {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
-        return launch_pdl(kernel, dim3((unsigned)blocks), dim3(256), (size_t)Cfg::SMEM_BYTES, st, (const uint4 *)in,
-                          (uint4 *)out, rows, scale * 64.0f, (const uint4 *)signs);
+        return launch_pdl(kernel, dim3((unsigned)blocks), dim3(Cfg::NW * 32), (size_t)Cfg::SMEM_BYTES, st,
+                          (const uint4 *)in, (uint4 *)out, rows, scale * 64.0f, (const uint4 *)signs);
     };
     return signs ? go(fwht_smem_kernel<DT, LOGN, true>) : go(fwht_smem_kernel<DT, LOGN, false>);
 }
@@ -469,7 +505,7 @@ static int launch_smem2(const void *in, void *out, uint64_t rows, float scale, c
     auto go = [&](auto kernel) -> int {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
-        return launch_pdl(kernel, dim3((unsigned)blocks), dim3(256), (size_t)Cfg::SMEM_BYTES, st, (const uint4 *)in,
+        return launch_pdl(kernel, dim3((unsigned)blocks), dim3(Cfg::NW * 32), (size_t)Cfg::SMEM_BYTES, st, (const uint4 *)in,
                           (uint4 *)out, rows, scale * 16.0f, (const uint4 *)signs);
     };
     return signs ? go(fwht_smem2_kernel<DT, LOGN, true>) : go(fwht_smem2_kernel<DT, LOGN, false>);
