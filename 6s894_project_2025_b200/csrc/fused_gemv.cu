@@ -637,6 +637,38 @@ gemv_f32_kernel(const float *W, const float *X, void *Y, int M, int N, int logn,
     slab_fwht_f32(hx, Bg * N, logn, tid, 256);
     for (int idx = tid; idx < Bg * N; idx += 256) hx[idx] *= scale;
     __syncthreads();
+    if ((N & 255) == 0) {
+        // one warp per row, 16-byte loads of W (two in flight per lane), up to 8 columns of H(X) per pass over the row
+        const float4 *hx4 = (const float4 *)hx;
+        const int nv = N >> 2;
+        for (int row = blockIdx.x * 8 + warp; row < M; row += gridDim.x * 8) {
+            const float4 *w4 = (const float4 *)(W + (size_t)row * N);
+            for (int c0 = 0; c0 < Bg; c0 += 8) {
+                float acc[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+                for (int k = lane; k < nv; k += 64) {
+                    const float4 wa = __ldg(w4 + k), wb = __ldg(w4 + k + 32);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        if (c0 + j < Bg) {
+                            const float4 ha = hx4[(size_t)(c0 + j) * nv + k], hb = hx4[(size_t)(c0 + j) * nv + k + 32];
+                            acc[j] = fmaf(wa.x, ha.x, fmaf(wa.y, ha.y, fmaf(wa.z, ha.z, fmaf(wa.w, ha.w, acc[j]))));
+                            acc[j] = fmaf(wb.x, hb.x, fmaf(wb.y, hb.y, fmaf(wb.z, hb.z, fmaf(wb.w, hb.w, acc[j]))));
+                        }
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    float s = acc[j];
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                    if (lane == 0 && c0 + j < Bg) store_out(Y, (size_t)row * B + b0 + c0 + j, s, out_dtype);
+                }
+            }
+        }
+        return;
+    }
     for (int row = blockIdx.x * 8 + warp; row < M; row += gridDim.x * 8) {
         const float *w = W + (size_t)row * N;
         for (int c0 = 0; c0 < Bg; c0 += 4) {
@@ -774,6 +806,10 @@ int launch_gemv(const void *W, const void *X, void *Y, int M, int N, int B, int 
         if (in_dtype != B200HT_F32) return B200HT_ERR_SIZE;  // bf16 path needs N >= 32
         int bg_max = (int)(kBudget / ((size_t)N * 4));
         if (bg_max < 1) bg_max = 1;
+        if (bg_max > 8) bg_max = 8;   // the row loop keeps at most 8 columns per pass over a row of W
+        // balanced column groups (W is streamed once per group); one wave of CTAs, as many per SM as the slab allows
+        const int ngroups = (B + bg_max - 1) / bg_max;
+        bg_max = (B + ngroups - 1) / ngroups;
         for (int b0 = 0; b0 < B; b0 += bg_max) {
             const int Bg = (B - b0) < bg_max ? (B - b0) : bg_max;
             const size_t smem = (size_t)Bg * N * 4;
@@ -781,7 +817,9 @@ int launch_gemv(const void *W, const void *X, void *Y, int M, int N, int B, int 
                                                  (int)smem);
             if (e != cudaSuccess) return (int)e;
             int grid = (M + 7) / 8;
-            const int cap = sm_count() * 2;
+            int per_sm = (int)((220 * 1024) / (smem + 1024));
+            per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
+            const int cap = sm_count() * per_sm;
             grid = grid < cap ? grid : cap;
             gemv_f32_kernel<<<grid, 256, smem, st>>>((const float *)W, (const float *)X, Y, M, N, logn, B, b0,
                                                      Bg, out_dtype, scale);
