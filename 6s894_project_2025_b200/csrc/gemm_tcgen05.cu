@@ -41,23 +41,25 @@ struct TcCfg {
     static constexpr int THREADS = 64 + 128 * MT;       // TMA warp, MMA warp, 4 * MT epilogue warps
 };
 
+// `ld` is the leading dimension of C in elements (N for M x N, M for N x M, larger when C is a block of a bigger
+// matrix).
 template <int OUT_DT, int LAYOUT>
-__device__ __forceinline__ void tc_store_chunk(void *C, int M, int N, int m, int n, const uint32_t (&r)[32])
+__device__ __forceinline__ void tc_store_chunk(void *C, int M, int N, size_t ld, int m, int n, const uint32_t (&r)[32])
 {
     if (m >= M || n >= N) return;
     if constexpr (LAYOUT == B200HT_OUT_NM) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
             if (n + j < N) {
-                const size_t idx = (size_t)(n + j) * M + m;
+                const size_t idx = (size_t)(n + j) * ld + m;
                 if constexpr (OUT_DT == B200HT_F32) ((float *)C)[idx] = __uint_as_float(r[j]);
                 else ((__nv_bfloat16 *)C)[idx] = __float2bfloat16_rn(__uint_as_float(r[j]));
             }
         }
     } else {
         if constexpr (OUT_DT == B200HT_F32) {
-            float *p = (float *)C + (size_t)m * N + n;
-            if ((N & 3) == 0 && n + 32 <= N) {
+            float *p = (float *)C + (size_t)m * ld + n;
+            if ((ld & 3) == 0 && n + 32 <= N) {
 #pragma unroll
                 for (int j = 0; j < 32; j += 4)
                     *(float4 *)(p + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
@@ -68,8 +70,8 @@ __device__ __forceinline__ void tc_store_chunk(void *C, int M, int N, int m, int
                     if (n + j < N) p[j] = __uint_as_float(r[j]);
             }
         } else {
-            __nv_bfloat16 *p = (__nv_bfloat16 *)C + (size_t)m * N + n;
-            if ((N & 7) == 0 && n + 32 <= N) {
+            __nv_bfloat16 *p = (__nv_bfloat16 *)C + (size_t)m * ld + n;
+            if ((ld & 7) == 0 && n + 32 <= N) {
 #pragma unroll
                 for (int j = 0; j < 32; j += 8) {
                     uint4 v;
@@ -105,7 +107,8 @@ __device__ __forceinline__ void tc_tile_coord(int tile, int mt, int nt, int &mb,
 template <int OUT_DT, int LAYOUT, int MT>
 __global__ void __launch_bounds__(TcCfg<MT>::THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmY,
-               const __grid_constant__ CUtensorMap tmC, int tma_store, void *C, int M, int N, int K, int *status)
+               const __grid_constant__ CUtensorMap tmC, int tma_store, void *C, int M, int N, int K, size_t ldc,
+               int ntiles_run, int pdl_mode, int *status)
 {
     using Cfg = TcCfg<MT>;
     constexpr int STAGES = Cfg::STAGES, STAGE_BYTES = Cfg::STAGE_BYTES, NACC = Cfg::NACC;
@@ -145,11 +148,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     const uint32_t tmem_base = *tmem_slot;
     // programmatic dependent launch: everything above overlapped the tail of the transform kernel that
     // produces the token operand; from here on its output is needed
-    pdl_launch_dependents();
-    pdl_wait();
+    // Programmatic dependent launch.  Mode 0: let the next kernel of the stream be scheduled at once, then wait for
+    // everything before this kernel.  A GEMM that is split into two launches (256-row tiles for the whole waves,
+    // 128-row tiles for the rest) uses mode 1 for the first -- the second launch is released only after this one has
+    // seen the transform complete -- and mode 2 for the second: it starts without waiting (its inputs are complete
+    // by then and its output block is disjoint from the first launch's) and waits for the first launch before it
+    // ends, so that later work in the stream still sees both finished.
+    if (pdl_mode == 1) {
+        pdl_wait();
+        pdl_launch_dependents();
+    } else {
+        pdl_launch_dependents();
+        if (pdl_mode == 0) pdl_wait();
+    }
 
     const int mt = (M + Cfg::BM - 1) / Cfg::BM, nt = (N + TC_BN - 1) / TC_BN;
-    const int ntiles = mt * nt;
+    const int ntiles = ntiles_run < mt * nt ? ntiles_run : mt * nt;   // tiles beyond it belong to a second launch
     const int kblocks = K / TC_BK;
 
     if (warp == 0) {
@@ -278,7 +292,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     uint32_t r[32];
                     tmem_ld32(taddr + c, r);
                     tmem_ld_wait();
-                    tc_store_chunk<OUT_DT, LAYOUT>(C, M, N, m, n0 + c, r);
+                    tc_store_chunk<OUT_DT, LAYOUT>(C, M, N, ldc, m, n0 + c, r);
                 }
             }
             tc_fence_before();
@@ -295,6 +309,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
     }
+    if (pdl_mode == 2 && threadIdx.x == 0) pdl_wait();
 }
 
 // ---------------------------------------------------------------------------
@@ -377,13 +392,13 @@ int encode_tmap_bf16_rows_chunks(CUtensorMap *map, const void *base, uint64_t ro
 }
 
 // Output map for the TMA-store epilogue: rows x cols of fp32 or bf16, box = 32 rows x 128 bytes, 128-byte swizzle.
-static int encode_tmap_out_2d(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, int dtype)
+static int encode_tmap_out_2d(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint64_t ld, int dtype)
 {
     EncodeTiledFn fn = get_encode_fn();
     if (!fn) return (int)cudaErrorNotSupported;
     const uint64_t esz = dtype == B200HT_F32 ? 4 : 2;
     const cuuint64_t dims[2] = {cols, rows};
-    const cuuint64_t strides[1] = {cols * esz};
+    const cuuint64_t strides[1] = {ld * esz};
     const cuuint32_t box[2] = {(cuuint32_t)(128 / esz), 32};
     const cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(map, dtype == B200HT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
@@ -400,7 +415,8 @@ static int sm_count_tc()
 }
 
 template <int OUT_DT, int LAYOUT, int MT>
-static int launch_tc_mt(const void *Y, const void *W, void *C, int M, int N, int K, cudaStream_t st)
+static int launch_tc_mt(const void *Y, const void *W, void *C, int M, int N, int K, size_t ldc, int skip_last_tiles,
+                        int pdl_mode, cudaStream_t st)
 {
     using Cfg = TcCfg<MT>;
     CUtensorMap tw, ty;
@@ -413,15 +429,17 @@ static int launch_tc_mt(const void *Y, const void *W, void *C, int M, int N, int
     int tma_store = 0;
     if (LAYOUT == B200HT_OUT_MN) {
         const uint64_t esz = OUT_DT == B200HT_F32 ? 4 : 2;
-        if (((uint64_t)N * esz) % 16 == 0 && encode_tmap_out_2d(&tc, C, (uint64_t)M, (uint64_t)N, OUT_DT) == 0) tma_store = 1;
+        if (((uint64_t)ldc * esz) % 16 == 0 && ((uintptr_t)C & 15u) == 0 &&
+            encode_tmap_out_2d(&tc, C, (uint64_t)M, (uint64_t)N, (uint64_t)ldc, OUT_DT) == 0)
+            tma_store = 1;
     }
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<OUT_DT, LAYOUT, MT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
-    const int tiles = ((M + Cfg::BM - 1) / Cfg::BM) * ((N + TC_BN - 1) / TC_BN);
+    const int tiles = ((M + Cfg::BM - 1) / Cfg::BM) * ((N + TC_BN - 1) / TC_BN) - skip_last_tiles;
     const int grid = tiles < sm_count_tc() ? tiles : sm_count_tc();
     return launch_pdl(gemm_tc_kernel<OUT_DT, LAYOUT, MT>, dim3(grid), dim3(Cfg::THREADS), (size_t)Cfg::SMEM_BYTES, st,
-                      tw, ty, tc, tma_store, C, M, N, K, status_word_ptr());
+                      tw, ty, tc, tma_store, C, M, N, K, ldc, tiles, pdl_mode, status_word_ptr());
 }
 
 template <int OUT_DT, int LAYOUT>
@@ -429,17 +447,45 @@ static int launch_tc(const void *Y, const void *W, void *C, int M, int N, int K,
 {
     // 256-row or 128-row CTA tiles: whichever needs less time in units of a 128-row tile, counting whole waves
     // over the SMs (a 256-row tile costs two units; 128-row tiles pay about 3 % more for operand traffic).
-    // B200HT_GEMM_MT=1|2 forces one of them (tuning knob).
+    // B200HT_GEMM_MT=1|2 forces one of them, B200HT_GEMM_SPLIT=0 disables the two-launch form (tuning knobs).
     static const int force_mt = [] {
         const char *e = std::getenv("B200HT_GEMM_MT");
         return e ? std::atoi(e) : 0;
     }();
+    static const bool allow_split = [] {
+        const char *e = std::getenv("B200HT_GEMM_SPLIT");
+        return !(e && e[0] == '0');
+    }();
+    const size_t ldc = LAYOUT == B200HT_OUT_MN ? (size_t)N : (size_t)M;
     const long sms = sm_count_tc();
     const long nt = (N + TC_BN - 1) / TC_BN;
-    const long tiles128 = (long)((M + 127) / 128) * nt, tiles256 = (long)((M + 255) / 256) * nt;
-    const double cost128 = 1.03 * (double)((tiles128 + sms - 1) / sms), cost256 = 2.0 * (double)((tiles256 + sms - 1) / sms);
+    const long mt256 = (M + 255) / 256;
+    const long tiles128 = (long)((M + 127) / 128) * nt, tiles256 = mt256 * nt;
+    // With 256-row tiles the last, partial wave costs a whole tile time.  When the tiles of that wave form a rectangle
+    // at the end of the tile order (rows of the last group of 16 row blocks x the last token blocks) and fit one wave
+    // as 128-row tiles, they can be computed by a second launch with 128-row tiles: half the time for the tail.
+    const long rem = tiles256 % sms;
+    const long gl = mt256 % TC_GROUP_M ? mt256 % TC_GROUP_M : TC_GROUP_M;   // row blocks in the last group
+    const bool can_split = allow_split && tiles256 > sms && rem > 0 && 2 * rem <= sms && (rem <= gl || rem % gl == 0) &&
+                           rem < gl * nt;
+    const double cost128 = 1.03 * (double)((tiles128 + sms - 1) / sms);
+    const double cost256 = can_split ? 2.0 * (double)(tiles256 / sms) + 1.03 : 2.0 * (double)((tiles256 + sms - 1) / sms);
     const bool big = force_mt ? force_mt == 2 : (tiles256 >= sms && cost256 <= cost128);
-    return big ? launch_tc_mt<OUT_DT, LAYOUT, 2>(Y, W, C, M, N, K, st) : launch_tc_mt<OUT_DT, LAYOUT, 1>(Y, W, C, M, N, K, st);
+    if (!big) return launch_tc_mt<OUT_DT, LAYOUT, 1>(Y, W, C, M, N, K, ldc, 0, 0, st);
+    if (can_split && !force_mt) {
+        const long cols = rem <= gl ? 1 : rem / gl;          // token blocks of the rectangle
+        const long rows = rem <= gl ? rem : gl;              // 256-row blocks of the rectangle
+        const long row_off = (mt256 - rows) * 256, tok_off = (nt - cols) * TC_BN;
+        int rc = launch_tc_mt<OUT_DT, LAYOUT, 2>(Y, W, C, M, N, K, ldc, (int)rem, 1, st);
+        if (rc) return rc;
+        const size_t esz = OUT_DT == B200HT_F32 ? 4 : 2;
+        const size_t coff = LAYOUT == B200HT_OUT_MN ? (size_t)row_off * ldc + (size_t)tok_off : (size_t)tok_off * ldc + (size_t)row_off;
+        return launch_tc_mt<OUT_DT, LAYOUT, 1>((const unsigned char *)Y + (size_t)tok_off * K * 2,
+                                               (const unsigned char *)W + (size_t)row_off * K * 2,
+                                               (unsigned char *)C + coff * esz, (int)(M - row_off), (int)(N - tok_off), K, ldc,
+                                               0, 2, st);
+    }
+    return launch_tc_mt<OUT_DT, LAYOUT, 2>(Y, W, C, M, N, K, ldc, 0, 0, st);
 }
 
 int launch_gemm_bf16_tcgen05(const void *Y, const void *W, void *C, int M, int N, int K, int out_dtype,
