@@ -1,4 +1,5 @@
 // Version, error text, device check and the device status word.
+#include <atomic>
 #include <mutex>
 
 #include "tc_common.cuh"
@@ -6,6 +7,9 @@
 namespace b200ht {
 
 __device__ int g_status_word = 0;
+
+static std::atomic<unsigned long long> g_launches{0};
+void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 int *status_word_ptr()
 {
@@ -35,6 +39,11 @@ int check_device()
 }  // namespace b200ht
 
 extern "C" int b200ht_version(void) { return 100; }
+
+extern "C" unsigned long long b200ht_launch_count(void)
+{
+    return b200ht::g_launches.load(std::memory_order_relaxed);
+}
 
 extern "C" const char *b200ht_error_string(int code)
 {
@@ -112,6 +121,7 @@ extern "C" int b200ht_selftest_wait_timeout(unsigned int limit_us, void *stream)
     cudaStream_t st = (cudaStream_t)stream;
     e = cudaMemsetAsync(flag, 0, sizeof(int), st);
     if (e != cudaSuccess) return (int)e;
+    note_launch();
     wait_timeout_probe_kernel<<<1, 32, 0, st>>>((unsigned long long)limit_us * 1000ull, status_word_ptr(), flag);
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;

@@ -40,9 +40,13 @@ int check_device();
 // kernel launched this way executes pdl_wait() before it touches global memory, which
 // blocks until all earlier work of the stream has completed and is visible, and
 // pdl_launch_dependents() as early as it likes.
+// Every kernel launch of the library is counted (b200ht_launch_count reports the total).
+void note_launch();
+
 template <typename... KArgs, typename... Args>
 inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args)
 {
+    note_launch();
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;

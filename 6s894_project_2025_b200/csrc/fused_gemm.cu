@@ -129,6 +129,7 @@ static int launch_sgemm(const float *A, const float *Bm, void *C, int M, int N, 
 {
     dim3 grid((N + SG_BN - 1) / SG_BN, (M + SG_BM - 1) / SG_BM);
     const int vec = ((K & 3) == 0 && aligned16(A) && aligned16(Bm)) ? 1 : 0;
+    note_launch();
     if (out_dtype == B200HT_F32) {
         if (out_layout == B200HT_OUT_MN)
             sgemm_nt_kernel<B200HT_F32, B200HT_OUT_MN><<<grid, 256, 0, st>>>(A, Bm, C, M, N, K, vec);
@@ -205,6 +206,8 @@ static int launch_fp32_tc(const float *W, const float *Y, void *C, int M, int N,
     __nv_bfloat16 *Ys = (__nv_bfloat16 *)(ws + ((((size_t)M * K * 12) + 255) & ~(size_t)255));
     const size_t wv = (size_t)M * K / 4, yv = (size_t)N * K / 4;
     const int cap = 148 * 16;
+    note_launch();
+    note_launch();
     split3_kernel<<<(unsigned)((wv + 255) / 256 < (size_t)cap ? (wv + 255) / 256 : cap), 256, 0, st>>>(
         (const float4 *)W, Ws, wv, K, 1);
     split3_kernel<<<(unsigned)((yv + 255) / 256 < (size_t)cap ? (yv + 255) / 256 : cap), 256, 0, st>>>(

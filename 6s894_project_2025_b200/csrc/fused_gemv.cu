@@ -706,6 +706,7 @@ static int launch_bf16_nt(const void *W, const void *X, void *Y, int M, int N, i
     if (e != cudaSuccess) return (int)e;
     const int tiles = (M + 15) / 16;
     const int grid = tiles < sm_count() ? tiles : sm_count();
+    note_launch();
     gemv_bf16_kernel<NT><<<grid, 256, smem, st>>>((const __nv_bfloat16 *)W, (const __nv_bfloat16 *)X, Y, M,
                                                   N, logn, B, b0, Bg, gc, out_dtype, scale);
     return (int)cudaGetLastError();
@@ -821,6 +822,7 @@ int launch_gemv(const void *W, const void *X, void *Y, int M, int N, int B, int 
             per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
             const int cap = sm_count() * per_sm;
             grid = grid < cap ? grid : cap;
+            note_launch();
             gemv_f32_kernel<<<grid, 256, smem, st>>>((const float *)W, (const float *)X, Y, M, N, logn, B, b0,
                                                      Bg, out_dtype, scale);
             e = cudaGetLastError();

@@ -520,6 +520,7 @@ static int launch_b16(const void *in, void *out, uint64_t rows, int logn, float 
     case 2: {
         const uint64_t blocks = (rows + 255) / 256;
         if (blocks > 0x7fffffffull) return B200HT_ERR_SIZE;
+        note_launch();
         fwht_tiny_kernel<DT><<<(unsigned)blocks, 256, 0, st>>>((const uint16_t *)in, (uint16_t *)out, rows,
                                                               1 << logn, scale, (const uint16_t *)signs);
         return (int)cudaGetLastError();
@@ -551,6 +552,7 @@ int launch_fwht_f32(const float *in, float *out, uint64_t rows, int logn, float 
     const int smem = slab * 4;
     cudaError_t e = cudaFuncSetAttribute(fwht_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
+    note_launch();
     fwht_f32_kernel<<<(unsigned)blocks, 256, smem, st>>>(in, out, rows, logn, slab_rows, scale);
     return (int)cudaGetLastError();
 }

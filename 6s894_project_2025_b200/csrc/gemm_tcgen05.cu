@@ -493,6 +493,7 @@ int launch_gemm_bf16_tcgen05(const void *Y, const void *W, void *C, int M, int N
 {
     if (K < TC_BK) {
         dim3 blk(32, 8), grd((N + 31) / 32, (M + 7) / 8);
+        note_launch();
         gemm_bf16_smallk_kernel<<<grd, blk, 0, st>>>((const __nv_bfloat16 *)Y, (const __nv_bfloat16 *)W, C, M, N, K,
                                                      out_dtype, out_layout);
         return (int)cudaGetLastError();

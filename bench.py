@@ -357,11 +357,13 @@ def run_gpu_arm(args):
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    launches0 = int(pkg._lib.load().b200ht_launch_count())
     e0.record()
     for _ in range(args.steps):
         step()
     e1.record()
     barrier()
+    gpu_launches = int(pkg._lib.load().b200ht_launch_count()) - launches0   # kernels of this rank in the timed region
     clocks = sampler.stop() if rank == 0 else None
     ms_local = e0.elapsed_time(e1) / args.steps
     status = pkg.device_status()
@@ -452,7 +454,7 @@ def run_gpu_arm(args):
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": X.numel() * 2 * world, "d2h_bytes_per_step": C.numel() * 2 * world},
-            "gpu_launches": 2 * args.steps,
+            "gpu_launches": gpu_launches,
             "clocks": clocks,
         }
         print(json.dumps(line))

@@ -170,6 +170,12 @@ int b200ht_fused_gemv(const void *W, const void *X, void *Y, int M, int N, int B
                       int in_dtype, int out_dtype, float scale, void *stream);
 
 /*
+ * Number of kernels this library has launched in the calling process so far (all entry points, all streams).
+ * A benchmark reads it before and after a timed region to report its launch count.  No counterpart in the reference.
+ */
+unsigned long long b200ht_launch_count(void);
+
+/*
  * Device-side status word of the calling thread's current device: 0, or the
  * B200HT_ERR_TIMEOUT code left by a kernel whose bounded wait on an mbarrier
  * expired.  Synchronises the device.  `clear` != 0 resets it.  The reference has
