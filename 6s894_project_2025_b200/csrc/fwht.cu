@@ -129,7 +129,7 @@ struct SmemCfg {
     static constexpr int CPR = 1 << Q;
     static constexpr int NCHUNK = SLAB_ROWS * CPR;
     static constexpr int SMEM_BYTES = NCHUNK * 33 * 16;
-    static constexpr int NW = LOGN == 13 ? 4 : 8;   // warps per CTA (measured: 4 is 2 % faster at n = 8192, 11 % slower at 16384)
+    static constexpr int NW = LOGN <= 14 ? 4 : 8;   // warps per CTA (measured: 4 with the warp-local copy-out is 2 % faster at n = 8192 and 16384)
 };
 
 template <int DT, int LOGN, bool SG>
@@ -189,11 +189,12 @@ __global__ void __launch_bounds__(SmemCfg<LOGN>::NW * 32) fwht_smem_kernel(const
     make_hfrag<DT>(A2, lane, M2, 0.5f);
     constexpr int J = Q > 5 ? (1 << (Q - 5)) : 1;
     const int nitems = Q >= 5 ? rows_here * 32 : rows_here * 16;
-    // Q == 5 (n = 8192, one row per CTA, 4 warps): a warp takes SPW = 8 consecutive slots, so that it alone writes, and afterwards reads,
+    // n = 8192, 16384 (one row per CTA, 4 warps): a warp takes SPW = 8 consecutive slots, so that it alone writes, and afterwards reads,
     // SPW*16 contiguous bytes of every chunk and no CTA-wide barrier is needed before the copy-out
     constexpr int SPW = 32 / NW;
-    for (int it = 0; it < (Q == 5 ? SPW : (nitems - warp + NW - 1) / NW); ++it) {
-        const int item = Q == 5 ? warp * SPW + it : warp + it * NW;
+    constexpr bool LOCAL_OUT = NW == 4;   // n = 8192, 16384: one row per CTA, SPW = 8
+    for (int it = 0; it < (LOCAL_OUT ? SPW : (nitems - warp + NW - 1) / NW); ++it) {
+        const int item = LOCAL_OUT ? warp * SPW + it : warp + it * NW;
         int slot, chunk0;
         if constexpr (Q >= 5) {
             slot = item & 31;
@@ -231,7 +232,7 @@ __global__ void __launch_bounds__(SmemCfg<LOGN>::NW * 32) fwht_smem_kernel(const
             sm[(chunk0 + 32 * j) * 33 + slot] = r;
         }
     }
-    if constexpr (Q == 5) {
+    if constexpr (LOCAL_OUT) {
         __syncwarp();
         // pass 3, warp-local: 32/SPW chunks x SPW slots per instruction, four instructions in flight
         constexpr int CPI = 32 / SPW;
