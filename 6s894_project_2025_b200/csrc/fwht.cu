@@ -8,10 +8,8 @@
 // below the memory time; data moves with 16-byte, fully coalesced accesses.
 //
 //   n = 8 .. 2048   fwht_reg_kernel : a warp keeps whole rows in registers
-//   n = 4096        fwht_smem2_kernel: a CTA keeps a slab of rows in shared memory;
-//                     index bits 0..9 in pass 1 (tensor cores + fp32), bits 10, 11 in
-//                     pass 2 (fp32 register butterflies)
-//   n = 8192, 16384 fwht_smem_kernel: padded shared memory; low 8 index bits in pass
+//   n = 4096..16384 fwht_smem_kernel: a slab of 32 or 64 chunks (two rows of 4096, one row
+//                     of 8192 or 16384) in padded shared memory; low 8 index bits in pass
 //                     1, the rest in pass 2, both through rot8
 //   n = 32768       fwht_tc_kernel (fwht_tcgen05.cu): tcgen05 + TMEM; falls back to
 //                     fwht_smem_kernel for buffers that are not 128-byte aligned
@@ -113,14 +111,19 @@ __global__ void __launch_bounds__(256) fwht_reg_kernel(const uint4 *in, uint4 *o
 }
 
 // ---------------------------------------------------------------------------
-// n = 8192, 16384 (and 32768 for unaligned buffers), 16-bit: a CTA of 4 or 8 warps holds a slab of SLAB_ROWS rows in
-// shared memory.  Chunk c (256 elements = 32 vectors) sits at vector offset 33*c
-// so that both the contiguous accesses of pass 1 and the chunk-strided accesses
-// of pass 2 are bank-conflict free.
-//   pass 1: every chunk: index bits 0..7, result rounded to 16 bit into smem
-//   pass 2: index bits 8..LOGN-1: five of them on the lanes through rot8 with
-//           identity on the in-lane bits, the rest as fp32 register butterflies
-//   pass 3: coalesced copy-out
+// n = 4096, 8192, 16384 (and 32768 for unaligned buffers or with a sign diagonal), 16-bit: a CTA of 4 warps (8 at
+// n = 32768) holds a slab of 32 chunks or more in shared memory: two rows of 4096, one row otherwise.  Chunk c (256
+// elements = 32 vectors) sits at vector offset 33*c so that both the contiguous accesses of pass 1 and the
+// chunk-strided accesses of pass 2 are bank-conflict free.
+//   pass 1: every chunk: index bits 0..7, eight 16-byte loads in flight per lane, result rounded to 16 bit into smem
+//   pass 2: index bits 8..LOGN-1: the lanes carry five chunk-index bits and go through rot8 with identity on the
+//           in-lane bits (and, at n = 4096, on the lane bit that selects the row); further bits are fp32 register
+//           butterflies.  With 4 warps a warp owns 8 consecutive vectors of every chunk.
+//   pass 3: copy-out, 128 contiguous bytes per chunk and warp, by the warp that wrote them (no CTA barrier); with 8
+//           warps a CTA barrier and whole chunks
+// Measured (16384 rows, TB/s): 6.46 / 6.70 / 6.32 at n = 4096 / 8192 / 16384.  Earlier variants: four loads in flight
+// 5.4 / 6.2 / 6.0; a second pass without tensor cores (fp32 butterflies and shuffles) 6.0 at n = 4096 and slower
+// beyond; whole rows in registers at n = 4096 4.7.
 // ---------------------------------------------------------------------------
 template <int LOGN>
 struct SmemCfg {
@@ -184,25 +187,22 @@ __global__ void __launch_bounds__(SmemCfg<LOGN>::NW * 32) fwht_smem_kernel(const
     __syncthreads();
 
     // pass 2: lanes <-> chunk-index bits 0..4 of the row (element bits 8..12)
+    // A slab always holds at least 32 chunks: for n = 4096 these are two rows, and the lane bit that selects the row
+    // is left alone (identity in the second constant), so the slab goes through the same code as one row of 8192.
+    static_assert(Q >= 4, "the slab kernel is written for n >= 4096");
     constexpr unsigned M2 = Q >= 5 ? 7u : 3u;
     make_hfrag<DT>(A1, lane, 6u, 0.5f);
     make_hfrag<DT>(A2, lane, M2, 0.5f);
     constexpr int J = Q > 5 ? (1 << (Q - 5)) : 1;
-    const int nitems = Q >= 5 ? rows_here * 32 : rows_here * 16;
+    const int nitems = 32;
     // n = 8192, 16384 (one row per CTA, 4 warps): a warp takes SPW = 8 consecutive slots, so that it alone writes, and afterwards reads,
     // SPW*16 contiguous bytes of every chunk and no CTA-wide barrier is needed before the copy-out
     constexpr int SPW = 32 / NW;
     constexpr bool LOCAL_OUT = NW == 4;   // n = 8192, 16384: one row per CTA, SPW = 8
     for (int it = 0; it < (LOCAL_OUT ? SPW : (nitems - warp + NW - 1) / NW); ++it) {
         const int item = LOCAL_OUT ? warp * SPW + it : warp + it * NW;
-        int slot, chunk0;
-        if constexpr (Q >= 5) {
-            slot = item & 31;
-            chunk0 = (item >> 5) * CPR + lane;
-        } else {
-            slot = 2 * (item & 15) + (lane >> 4);
-            chunk0 = (item >> 4) * CPR + (lane & 15);
-        }
+        const int slot = item & 31;
+        const int chunk0 = lane;
         float o[J][8];
         uint4 tv[J];
 #pragma unroll
@@ -254,165 +254,6 @@ __global__ void __launch_bounds__(SmemCfg<LOGN>::NW * 32) fwht_smem_kernel(const
     } else {
         __syncthreads();
         for (int c = warp; c < chunks_here; c += NW) st_stream(gout + c * 32 + lane, sm[c * 33 + lane]);
-    }
-}
-
-// ---------------------------------------------------------------------------
-// n = 4096 (written for 4096 .. 32768), 16-bit, second variant: a CTA of 4 warps
-// holds a 32 KB slab of rows in shared memory, chunk c (256 elements = 32 vectors)
-// at vector offset 32c.
-//   pass 1: a warp takes 4 consecutive chunks (two such groups at a time): index bits 0..7 through rot8 (the
-//           only tensor-core work: 4 mma.sync per 256 elements, as for n <= 2048),
-//           bits 8, 9 as fp32 butterflies across the 4 chunks, result rounded to
-//           16 bit into shared memory
-//   pass 2: index bits 10..LOGN-1 without tensor cores: a thread loads 4 vectors
-//           that differ in two of those bits (fp32 register butterflies), further
-//           bits sit on the high lane bits (shuffle butterflies); the low lane
-//           bits are consecutive vectors, so shared-memory reads are conflict free
-//           and the results go straight to global memory in segments of 64..512
-//           contiguous bytes.
-// The SM sustains about one mma.sync.m16n8k16 per 5.5 cycles, which the two-rot8
-// kernel above reaches at HBM speed; keeping the second pass off the tensor pipe
-// wins at n = 4096 (two register bits, no shuffles: 5.69 vs 5.41 TB/s) and loses
-// at n >= 8192, where the extra bits need shuffles (5.80 vs 6.06, 5.46 vs 5.94).
-// ---------------------------------------------------------------------------
-template <int LOGN>
-struct Smem2Cfg {
-    static constexpr int NW = 4;    // warps per CTA
-    static constexpr int G = 2;     // groups of 4 chunks a warp loads at once (8 x 16 bytes in flight per lane);
-                                    // measured at n = 4096: (NW, G) = (4, 2) 6.0 TB/s, (8, 1) 5.8, (4, 1) 5.4
-    static constexpr int SLAB_ELEMS = LOGN >= 15 ? (1 << 15) : (1 << 14);
-    static constexpr int SLAB_ROWS = SLAB_ELEMS >> LOGN;
-    static constexpr int CPR = 1 << (LOGN - 8);             // chunks per row
-    static constexpr int NCHUNK = SLAB_ROWS * CPR;
-    static constexpr int SMEM_BYTES = NCHUNK * 32 * 16;
-    static constexpr int Q = LOGN - 10;                     // index bits left for pass 2
-    static constexpr int RB = Q < 2 ? Q : 2;                // ... in registers
-    static constexpr int SB = Q - RB;                       // ... on the high lane bits
-};
-
-template <int DT, int LOGN, bool SG>
-__global__ void __launch_bounds__(Smem2Cfg<LOGN>::NW * 32) fwht_smem2_kernel(const uint4 *in, uint4 *out, uint64_t rows,
-                                                         float mult, const uint4 *signs)
-{
-    using Cfg = Smem2Cfg<LOGN>;
-    constexpr int CPR = Cfg::CPR, RB = Cfg::RB, SB = Cfg::SB, J = 1 << RB;
-    extern __shared__ uint4 sm[];
-    pdl_launch_dependents();
-    pdl_wait();
-    const int lane = threadIdx.x & 31;
-    const int warp = threadIdx.x >> 5;
-    const uint64_t row0 = (uint64_t)blockIdx.x * Cfg::SLAB_ROWS;
-    const int rows_here = (int)((rows - row0) < (uint64_t)Cfg::SLAB_ROWS ? (rows - row0)
-                                                                          : (uint64_t)Cfg::SLAB_ROWS);
-    const int chunks_here = rows_here * CPR;
-    const uint4 *gin = in + row0 * (uint64_t)(CPR * 32);
-    uint4 *gout = out + row0 * (uint64_t)(CPR * 32);
-
-    // ---- pass 1
-    {
-        uint32_t A1[4], A2[4];
-        make_hfrag<DT>(A1, lane, 15u, 0.25f);
-        make_hfrag<DT>(A2, lane, 15u, 0.25f);
-        constexpr int G = Cfg::G, NW = Cfg::NW;   // a warp takes G groups of 4 chunks at once: 4*G loads in flight per lane
-        for (int g0 = warp * 4 * G; g0 < chunks_here; g0 += NW * 4 * G) {
-            uint4 v[4 * G];
-#pragma unroll
-            for (int u = 0; u < 4 * G; ++u)
-                v[u] = g0 + u < chunks_here ? ld_stream(gin + (g0 + u) * 32 + lane) : make_uint4(0, 0, 0, 0);
-            if constexpr (SG) {
-#pragma unroll
-                for (int u = 0; u < 4 * G; ++u)
-                    if (g0 + u < chunks_here) flip_signs(v[u], signs, (uint32_t)(((g0 + u) & (CPR - 1)) * 32 + lane));
-            }
-            float o[4 * G][8];
-            rot8x<DT, 4 * G>(v, o, A1, A2);
-#pragma unroll
-            for (int gg = 0; gg < G; ++gg) {
-#pragma unroll
-                for (int s = 1; s < 4; s <<= 1) {
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        if (!(u & s)) {
-#pragma unroll
-                            for (int e = 0; e < 8; ++e) {
-                                const float x = o[gg * 4 + u][e], y = o[gg * 4 + (u | s)][e];
-                                o[gg * 4 + u][e] = x + y;
-                                o[gg * 4 + (u | s)][e] = x - y;
-                            }
-                        }
-                    }
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < 4 * G; ++u) {
-                if (g0 + u < chunks_here) {
-                    uint4 r;
-                    r.x = pack2<DT>(o[u][0], o[u][1]);
-                    r.y = pack2<DT>(o[u][2], o[u][3]);
-                    r.z = pack2<DT>(o[u][4], o[u][5]);
-                    r.w = pack2<DT>(o[u][6], o[u][7]);
-                    sm[(g0 + u) * 32 + lane] = r;
-                }
-            }
-        }
-    }
-    __syncthreads();
-
-    // ---- pass 2: chunk-index bits 2.. of the row (element bits 10..)
-    constexpr int SLOTS = 32 >> SB;                // consecutive vectors handled by the low lane bits
-    const int lane_lo = lane & (SLOTS - 1), lane_hi = lane >> (5 - SB);
-    const int ntasks = rows_here * 4 * (1 << SB);  // (row, chunk low 2 bits, slot block)
-    for (int task = warp; task < ntasks; task += Cfg::NW) {
-        const int sblk = task & ((1 << SB) - 1);
-        const int clow = (task >> SB) & 3;
-        const int row = task >> (SB + 2);
-        const int slot = sblk * SLOTS + lane_lo;
-        const int chunk0 = row * CPR + clow + 4 * (J * lane_hi);   // + 4 * j
-        float f[J][8];
-#pragma unroll
-        for (int j = 0; j < J; ++j) {
-            const uint4 t = sm[(chunk0 + 4 * j) * 32 + slot];
-            const float2 a = unpack2<DT>(t.x), b = unpack2<DT>(t.y), c = unpack2<DT>(t.z), d = unpack2<DT>(t.w);
-            f[j][0] = a.x; f[j][1] = a.y; f[j][2] = b.x; f[j][3] = b.y;
-            f[j][4] = c.x; f[j][5] = c.y; f[j][6] = d.x; f[j][7] = d.y;
-        }
-#pragma unroll
-        for (int s = 1; s < J; s <<= 1) {
-#pragma unroll
-            for (int j = 0; j < J; ++j) {
-                if (!(j & s)) {
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        const float x = f[j][e], y = f[j | s][e];
-                        f[j][e] = x + y;
-                        f[j | s][e] = x - y;
-                    }
-                }
-            }
-        }
-#pragma unroll
-        for (int sb = 0; sb < SB; ++sb) {
-            const int m = 1 << (5 - SB + sb);
-            const bool upper = (lane & m) != 0;
-#pragma unroll
-            for (int j = 0; j < J; ++j) {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const float other = __shfl_xor_sync(0xffffffffu, f[j][e], m);
-                    f[j][e] = upper ? other - f[j][e] : f[j][e] + other;
-                }
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < J; ++j) {
-            uint4 r;
-            r.x = pack2<DT>(f[j][0] * mult, f[j][1] * mult);
-            r.y = pack2<DT>(f[j][2] * mult, f[j][3] * mult);
-            r.z = pack2<DT>(f[j][4] * mult, f[j][5] * mult);
-            r.w = pack2<DT>(f[j][6] * mult, f[j][7] * mult);
-            st_stream(gout + (chunk0 + 4 * j) * 32 + slot, r);
-        }
     }
 }
 
@@ -497,21 +338,6 @@ static int launch_smem(const void *in, void *out, uint64_t rows, float scale, co
     return signs ? go(fwht_smem_kernel<DT, LOGN, true>) : go(fwht_smem_kernel<DT, LOGN, false>);
 }
 
-template <int DT, int LOGN>
-static int launch_smem2(const void *in, void *out, uint64_t rows, float scale, const void *signs, cudaStream_t st)
-{
-    using Cfg = Smem2Cfg<LOGN>;
-    const uint64_t blocks = (rows + Cfg::SLAB_ROWS - 1) / Cfg::SLAB_ROWS;
-    if (blocks > 0x7fffffffull) return B200HT_ERR_SIZE;
-    auto go = [&](auto kernel) -> int {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
-        if (e != cudaSuccess) return (int)e;
-        return launch_pdl(kernel, dim3((unsigned)blocks), dim3(Cfg::NW * 32), (size_t)Cfg::SMEM_BYTES, st, (const uint4 *)in,
-                          (uint4 *)out, rows, scale * 16.0f, (const uint4 *)signs);
-    };
-    return signs ? go(fwht_smem2_kernel<DT, LOGN, true>) : go(fwht_smem2_kernel<DT, LOGN, false>);
-}
-
 template <int DT>
 static int launch_b16(const void *in, void *out, uint64_t rows, int logn, float scale, const void *signs,
                       cudaStream_t st)
@@ -535,7 +361,7 @@ static int launch_b16(const void *in, void *out, uint64_t rows, int logn, float 
     case 9: return launch_reg<DT, 9>(in, out, rows, scale, signs, st);
     case 10: return launch_reg<DT, 10>(in, out, rows, scale, signs, st);
     case 11: return launch_reg<DT, 11>(in, out, rows, scale, signs, st);
-    case 12: return launch_smem2<DT, 12>(in, out, rows, scale, signs, st);
+    case 12: return launch_smem<DT, 12>(in, out, rows, scale, signs, st);
     case 13: return launch_smem<DT, 13>(in, out, rows, scale, signs, st);
     case 14: return launch_smem<DT, 14>(in, out, rows, scale, signs, st);
     case 15: return launch_smem<DT, 15>(in, out, rows, scale, signs, st);
