@@ -58,3 +58,29 @@ def test_cuda_graph_capture_and_replay(pkg):
     for a, b in zip(got, expect):
         assert torch.equal(a, b)
     assert pkg.device_status() == 0
+
+
+@pytest.mark.gpu
+def test_cuda_graph_with_the_two_launch_gemm(pkg):
+    """A shape whose 256-row tiles leave a partial wave (16 x 10 = 160 tiles on 148 SMs): the contraction is two
+    launches tied together by programmatic dependencies.  Captured in a graph and replayed, with the transform in
+    front and another call behind, it must give the eager result bit for bit."""
+    g = torch.Generator(device="cuda").manual_seed(6)
+    X = torch.randn(2560, 64, generator=g, device="cuda").bfloat16()
+    W = torch.randn(4096, 64, generator=g, device="cuda").bfloat16()
+    expect = pkg.fused_ht_gemm(X, W, out_layout="nm", out_dtype=torch.bfloat16)
+    expect2 = pkg.fused_ht_gemm(X, W)
+    ref = (W.float() @ pkg.hadamard_transform(X).float().t())
+    assert float((expect2 - ref).norm() / ref.norm()) < 2e-2
+    torch.cuda.synchronize()
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            got = pkg.fused_ht_gemm(X, W, out_layout="nm", out_dtype=torch.bfloat16)
+            got2 = pkg.fused_ht_gemm(X, W)
+        for _ in range(3):
+            graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(got, expect) and torch.equal(got2, expect2)
+    assert pkg.device_status() == 0
