@@ -11,6 +11,7 @@
 
 namespace b200ht {
 
+int launch_fwht_f32_split(const float *in, __nv_bfloat16 *split, uint64_t rows, uint32_t n, float scale, cudaStream_t st);
 int launch_fwht(const void *in, void *out, uint64_t rows, uint32_t n, int dtype, float scale, const void *signs,
                 cudaStream_t st);
 int launch_gemm_bf16_tcgen05(const void *Y, const void *W, void *C, int M, int N, int K, int out_dtype,
@@ -199,19 +200,20 @@ static size_t fp32_tc_workspace_bytes(int M, int N, int K)
 // K = 4096, 9.1e-6 at K = 8192 (FFMA kernel: 0.6e-6, 1.2e-6, 1.6e-6); beyond 4096 the margin to 1e-5 is gone.
 static bool fp32_tc_shape(int M, int N, int K) { return K >= 32 && K <= 4096 && (double)M * N * K >= 5e8; }
 
-static int launch_fp32_tc(const float *W, const float *Y, void *C, int M, int N, int K, int out_dtype, int out_layout,
-                          unsigned char *ws, cudaStream_t st)
+// X (fp32, untransformed) and W (fp32) -> C through the split contraction; `ws` is the part of the workspace behind
+// the fp32 H(X) area (which this path leaves unused: the transform kernel writes the split rows directly).
+static int launch_fp32_tc(const float *X, const float *W, void *C, int M, int N, int K, float scale, int out_dtype,
+                          int out_layout, unsigned char *ws, cudaStream_t st)
 {
     __nv_bfloat16 *Ws = (__nv_bfloat16 *)ws;
     __nv_bfloat16 *Ys = (__nv_bfloat16 *)(ws + ((((size_t)M * K * 12) + 255) & ~(size_t)255));
-    const size_t wv = (size_t)M * K / 4, yv = (size_t)N * K / 4;
+    int rc = launch_fwht_f32_split(X, Ys, (uint64_t)N, (uint32_t)K, scale, st);
+    if (rc) return rc;
+    const size_t wv = (size_t)M * K / 4;
     const int cap = 148 * 16;
-    note_launch();
     note_launch();
     split3_kernel<<<(unsigned)((wv + 255) / 256 < (size_t)cap ? (wv + 255) / 256 : cap), 256, 0, st>>>(
         (const float4 *)W, Ws, wv, K, 1);
-    split3_kernel<<<(unsigned)((yv + 255) / 256 < (size_t)cap ? (yv + 255) / 256 : cap), 256, 0, st>>>(
-        (const float4 *)Y, Ys, yv, K, 0);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     return launch_gemm_bf16_tcgen05(Ys, Ws, C, M, N, 6 * K, out_dtype, out_layout, st);
@@ -256,16 +258,15 @@ static int fused_gemm_entry(const void *X, const void *W, void *C, int M, int N,
     int rc = check_device();
     if (rc) return rc;
     cudaStream_t st = (cudaStream_t)stream;
+    // fp32: a workspace of the larger size (b200ht_fused_gemm_tc_workspace_bytes) selects the split-bf16 tensor-core
+    // contraction, the minimal one the exact FFMA kernel
+    if (in_dtype == B200HT_F32 && fp32_tc_shape(M, N, K) && workspace_bytes >= fp32_tc_workspace_bytes(M, N, K))
+        return launch_fp32_tc((const float *)X, (const float *)W, C, M, N, K, scale, out_dtype, out_layout,
+                              (unsigned char *)workspace + ((((size_t)N * K * 4) + 255) & ~(size_t)255), st);
     rc = launch_fwht(X, workspace, (uint64_t)N, (uint32_t)K, in_dtype, scale, signs, st);
     if (rc) return rc;
-    if (in_dtype == B200HT_F32) {
-        // a workspace of the larger size (b200ht_fused_gemm_tc_workspace_bytes) selects the split-bf16 tensor-core
-        // contraction, the minimal one the exact FFMA kernel
-        if (fp32_tc_shape(M, N, K) && workspace_bytes >= fp32_tc_workspace_bytes(M, N, K))
-            return launch_fp32_tc((const float *)W, (const float *)workspace, C, M, N, K, out_dtype, out_layout,
-                                  (unsigned char *)workspace + ((((size_t)N * K * 4) + 255) & ~(size_t)255), st);
+    if (in_dtype == B200HT_F32)
         return launch_sgemm((const float *)W, (const float *)workspace, C, M, N, K, out_dtype, out_layout, st);
-    }
     return launch_gemm_bf16_tcgen05(workspace, W, C, M, N, K, out_dtype, out_layout, st);
 }
 

@@ -284,8 +284,11 @@ __global__ void fwht_tiny_kernel(const uint16_t *in, uint16_t *out, uint64_t row
 // ---------------------------------------------------------------------------
 // fp32: exact butterflies on a slab of max(n, 2048) floats in shared memory.
 // ---------------------------------------------------------------------------
+// With `split` set the result is not stored as fp32 but as the six-block bf16 row of the tensor-core contraction of
+// fused_gemm.cu: every value y = y1 + y2 + y3 (three bf16 terms, exact), row layout [y3 y1 y2 y2 y1 y1], each block
+// n elements long.
 __global__ void __launch_bounds__(256) fwht_f32_kernel(const float *in, float *out, uint64_t rows,
-                                                       int logn, int slab_rows, float scale)
+                                                       int logn, int slab_rows, float scale, __nv_bfloat16 *split)
 {
     extern __shared__ float sf[];
     const int n = 1 << logn;
@@ -297,7 +300,34 @@ __global__ void __launch_bounds__(256) fwht_f32_kernel(const float *in, float *o
     for (int i = threadIdx.x; i < total; i += blockDim.x) sf[i] = gin[i];
     __syncthreads();
     slab_fwht_f32(sf, total, logn, threadIdx.x, blockDim.x);
-    for (int i = threadIdx.x; i < total; i += blockDim.x) gout[i] = sf[i] * scale;
+    if (!split) {
+        for (int i = threadIdx.x; i < total; i += blockDim.x) gout[i] = sf[i] * scale;
+        return;
+    }
+    __syncthreads();
+    for (int i4 = threadIdx.x; i4 < total / 4; i4 += blockDim.x) {   // n >= 32 on this path: rows are multiples of 4
+        const float4 v = ((const float4 *)sf)[i4];
+        const float a[4] = {v.x * scale, v.y * scale, v.z * scale, v.w * scale};
+        uint32_t h[3][4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float r = a[e];
+#pragma unroll
+            for (int j = 0; j < 3; ++j) {
+                const __nv_bfloat16 b = __float2bfloat16_rn(r);
+                h[j][e] = (uint32_t)__bfloat16_as_ushort(b);
+                r -= __bfloat162float(b);
+            }
+        }
+        uint2 t[3];
+#pragma unroll
+        for (int j = 0; j < 3; ++j) t[j] = make_uint2(h[j][0] | (h[j][1] << 16), h[j][2] | (h[j][3] << 16));
+        const int idx = i4 * 4, row = idx >> logn, k = idx & (n - 1);
+        __nv_bfloat16 *o = split + (row0 + row) * (uint64_t)(6 * n) + k;
+        const int py[6] = {2, 0, 1, 1, 0, 0};
+#pragma unroll
+        for (int b = 0; b < 6; ++b) *(uint2 *)(o + (size_t)b * n) = t[py[b]];
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -369,7 +399,8 @@ static int launch_b16(const void *in, void *out, uint64_t rows, int logn, float 
     return B200HT_ERR_SIZE;
 }
 
-int launch_fwht_f32(const float *in, float *out, uint64_t rows, int logn, float scale, cudaStream_t st)
+int launch_fwht_f32(const float *in, float *out, uint64_t rows, int logn, float scale, cudaStream_t st,
+                    __nv_bfloat16 *split = nullptr)
 {
     const int n = 1 << logn;
     const int slab = n >= 2048 ? n : 2048;
@@ -380,8 +411,14 @@ int launch_fwht_f32(const float *in, float *out, uint64_t rows, int logn, float 
     cudaError_t e = cudaFuncSetAttribute(fwht_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     note_launch();
-    fwht_f32_kernel<<<(unsigned)blocks, 256, smem, st>>>(in, out, rows, logn, slab_rows, scale);
+    fwht_f32_kernel<<<(unsigned)blocks, 256, smem, st>>>(in, out, rows, logn, slab_rows, scale, split);
     return (int)cudaGetLastError();
+}
+
+// fp32 transform whose result goes straight into the split bf16 operand of the tensor-core contraction
+int launch_fwht_f32_split(const float *in, __nv_bfloat16 *split, uint64_t rows, uint32_t n, float scale, cudaStream_t st)
+{
+    return launch_fwht_f32(in, nullptr, rows, ilog2(n), scale, st, split);
 }
 
 int launch_fwht(const void *in, void *out, uint64_t rows, uint32_t n, int dtype, float scale, const void *signs,
