@@ -380,10 +380,12 @@ def run_gpu_arm(args):
     Xh = torch.empty(X.shape, dtype=X.dtype, pin_memory=True).copy_(X)
     Ch = torch.empty(C.shape, dtype=C.dtype, pin_memory=True)
 
-    pipe = pkg.HostPipeline(W, n_local, chunk_tokens=2048, n_streams=3, out_dtype=torch.bfloat16)
+    # chunks of 2048 tokens, but at least eight chunks per rank so that copy-in, compute and copy-out overlap
+    pipe = pkg.HostPipeline(W, n_local, chunk_tokens=max(256, min(2048, n_local // 8)), n_streams=3,
+                            out_dtype=torch.bfloat16)
 
     def e2e_step():
-        pipe(Xh, Ch)   # chunks of 2048 tokens: copy in, transform + GEMM, copy out, on three streams
+        pipe(Xh, Ch)   # per chunk: copy in, transform + GEMM, copy out, on three streams
 
     e2e_steps = max(2, min(args.steps, 5))
     e2e_step()
