@@ -240,6 +240,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             const int m0 = mb * Cfg::BM, n0 = nb * TC_BN;
             if (!mbar_wait(tfull_bar(acc), aph, abort_flag, status)) { ok = false; break; }
             tc_fence_after();
+            bool released = false;   // set where the accumulator is handed back before the stores
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (acc + h) * TC_BN;
             const int m = m0 + h * 128 + q * 32 + lane;
             if (LAYOUT == B200HT_OUT_MN && tma_store) {
@@ -292,35 +293,43 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 // registers are 2 bytes per lane and 64 contiguous bytes per instruction (measured: 9-11 us per
                 // 256 x 256 tile).  Instead the four warps of a 128-row half stage 32 tokens x 128 rows in shared
                 // memory (two buffers, one named barrier per chunk) and write them out as 16 bytes per lane, 256
-                // contiguous bytes per token (3.3-4.2 us per tile); the TMEM load of the next chunk is in flight
-                // meanwhile.
+                // contiguous bytes per token (3.3-4.2 us per tile).
                 unsigned char *stage_gen = gen_base + STAGES * STAGE_BYTES + h * 16384;
                 const int bar_id = 1 + h;
                 const int tok_sub = lane >> 4, seg = lane & 15;   // read-back: 2 tokens per instruction, 16 lanes each
-                auto flush = [&](const uint32_t (&r)[32], int c) {
-                    unsigned char *buf = stage_gen + ((c >> 5) & 1) * 8192;
-                    __nv_bfloat16 *col = (__nv_bfloat16 *)buf + q * 32 + lane;
+                // 1. drain the accumulator into registers (two bf16 per register: 128 registers for 256 tokens) and
+                //    hand the TMEM columns back at once, so the next tile's MMAs run underneath the stores
+                uint32_t pk[TC_BN / 2];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) col[j * 128] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                for (int cc = 0; cc < TC_BN / 32; ++cc) {
+                    uint32_t r[32];
+                    tmem_ld32(taddr + cc * 32, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        pk[cc * 16 + j] = pack2<B200HT_BF16>(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty_bar(acc));
+                released = true;
+                // 2. stage and store, 32 tokens at a time
+#pragma unroll
+                for (int cc = 0; cc < TC_BN / 32; ++cc) {
+                    unsigned char *buf = stage_gen + (cc & 1) * 8192;
+                    unsigned short *col = (unsigned short *)buf + q * 32 + lane;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        col[(2 * j) * 128] = (unsigned short)(pk[cc * 16 + j] & 0xffffu);
+                        col[(2 * j + 1) * 128] = (unsigned short)(pk[cc * 16 + j] >> 16);
+                    }
                     asm volatile("bar.sync %0, 128;\n" ::"r"(bar_id) : "memory");
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         const int j = q * 8 + i * 2 + tok_sub;   // token of the chunk written by this lane
                         const uint4 v = *(const uint4 *)(buf + j * 256 + seg * 16);
-                        *(uint4 *)((__nv_bfloat16 *)C + (size_t)(n0 + c + j) * ldc + m0 + h * 128 + seg * 8) = v;
+                        *(uint4 *)((__nv_bfloat16 *)C + (size_t)(n0 + cc * 32 + j) * ldc + m0 + h * 128 + seg * 8) = v;
                     }
-                };
-                uint32_t ra[32], rb[32];
-                tmem_ld32(taddr, ra);
-                tmem_ld_wait();
-#pragma unroll 1
-                for (int c = 0; c < TC_BN; c += 64) {
-                    tmem_ld32(taddr + c + 32, rb);
-                    flush(ra, c);
-                    tmem_ld_wait();
-                    if (c + 64 < TC_BN) tmem_ld32(taddr + c + 64, ra);
-                    flush(rb, c + 32);
-                    tmem_ld_wait();
                 }
             } else {
 #pragma unroll 1
@@ -331,9 +340,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     tc_store_chunk<OUT_DT, LAYOUT>(C, M, N, ldc, m, n0 + c, r);
                 }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(tempty_bar(acc));
+            if (!released) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty_bar(acc));
+            }
         }
         if (LAYOUT == B200HT_OUT_MN && tma_store && lane == 0)
             asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");   // this warp's stores are complete
