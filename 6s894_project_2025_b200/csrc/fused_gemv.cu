@@ -125,8 +125,10 @@ gemv_bf16_kernel(const __nv_bfloat16 *W, const __nv_bfloat16 *X, void *Y, int M,
 // bf16, 256 <= N <= 8192: the fast path.  16 warps per CTA, one CTA per SM,
 // every CTA owns a contiguous, balanced range of rows of W.
 //
-//  * From the first cycle the CTA streams its rows of W into a shared-memory
-//    ring with TMA tile loads (cp.async.bulk.tensor.3d over a [64 k][rows][N/64]
+//  * As soon as every warp has issued its loads of X (requests of one SM are
+//    served in order, and X must not queue behind W) the CTA streams its rows
+//    of W into a shared-memory ring with TMA tile loads, the first sixteen
+//    issued by sixteen lanes at once (cp.async.bulk.tensor.3d over a [64 k][rows][N/64]
 //    view of W: one op brings all rows of a row group x 256..1024 k as
 //    consecutive 128-byte-swizzled K-major tiles; completion is counted on an
 //    mbarrier per stage).  The copies hold no registers and no LSU slots, so HBM
