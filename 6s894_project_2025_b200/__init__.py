@@ -11,7 +11,7 @@ from .ops import (  # noqa: F401
     fused_ht_gemv,
     hadamard_transform,
 )
-from .partition import gather_result, shard_tokens, token_range  # noqa: F401
+from .partition import gather_result, gather_rows, row_range, shard_rows, shard_tokens, token_range  # noqa: F401
 from . import torchlib  # noqa: F401  (registers torch.ops.b200ht.*)
 
 __all__ = [
@@ -24,4 +24,7 @@ __all__ = [
     "token_range",
     "shard_tokens",
     "gather_result",
+    "row_range",
+    "shard_rows",
+    "gather_rows",
 ]

@@ -22,6 +22,7 @@ no collective on the data path), so total work is fixed: strong scaling.
   gemv      secondary block: fused GEMV, W 4096 x 4096 bf16, B = 1, 4, 16, GB/s
   c3        secondary block: fused W.H(X) at K=1024, 4096 tokens, M=4096, fp32 and bf16
   k4096     secondary block: fused W.H(X) at K=4096, M=16384, 16384 tokens, bf16, TFLOP/s
+  gemv_rows (N > 1 only) small-batch GEMV with the rows of W split over the GPUs and an all-gather of Y
   cpu_baseline  the reference's torch path (explicit Hadamard matmul, then
             matmul; bench/bench.py:44-59 of the reference) on the host cores,
             on a bounded slice of the same tokens
@@ -236,6 +237,39 @@ def time_gemv(pkg, torch, peaks, reps=20):
     return out
 
 
+def time_gemv_rows(pkg, torch, dist, rank, world, reps=20):
+    """Row-sharded small-batch GEMV (world > 1): every rank keeps M/world rows of W, computes its rows of Y and an
+    NCCL all-gather of M x B values assembles Y.  Timed per call including the all-gather; 8 rotating copies of the
+    W shard.  B = 4; W 4096 x 4096 (the C4 shape) and 28672 x 8192 (the C5 weight)."""
+    out = {}
+    g = torch.Generator(device="cuda").manual_seed(6)
+    for M, N in ((4096, 4096), (28672, 8192)):
+        a, b = pkg.row_range(M, rank, world)
+        Ws = [(torch.randn(b - a, N, generator=g, device="cuda") / math.sqrt(N)).bfloat16() for _ in range(8)]
+        X = torch.randn(N, 4, generator=g, device="cuda").bfloat16()
+
+        def call(Wt):
+            return pkg.gather_rows(pkg.fused_ht_gemv(Wt, X), M)
+
+        for Wt in Ws[:3]:
+            call(Wt)
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            for Wt in Ws:
+                call(Wt)
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / (reps * len(Ws))], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        out[f"{M}x{N}"] = {"ms": ms, "gbs_all_gpus": M * N * 2 / (ms * 1e-3) / 1e9, "rows_per_gpu": b - a}
+        del Ws
+    return out
+
+
 def time_c3(pkg, torch, peaks, reps=10):
     """Fused W.H(X) at K=1024, 4096 tokens, M=4096: fp32 (exact FFMA path), fp32 through the tensor cores
     (three bf16 terms per operand) and bf16 (tcgen05 path)."""
@@ -405,6 +439,7 @@ def run_gpu_arm(args):
     gemv = time_gemv(pkg, torch, peaks)
     c3 = time_c3(pkg, torch, peaks)
     k4096 = time_k4096(pkg, torch, peaks)
+    gemv_rows = time_gemv_rows(pkg, torch, dist, rank, world) if world > 1 else None
     if world > 1:
         agg = torch.tensor([fwht[k]["gbs"] for k in sorted(fwht, key=int)], device="cuda")
         dist.all_reduce(agg, op=dist.ReduceOp.SUM)
@@ -453,6 +488,7 @@ def run_gpu_arm(args):
             "gemv": gemv,
             "c3": c3,
             "k4096": k4096,
+            "gemv_rows": gemv_rows,
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": X.numel() * 2 * world, "d2h_bytes_per_step": C.numel() * 2 * world},

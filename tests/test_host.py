@@ -122,6 +122,12 @@ def test_two_rank_gloo_shard_and_gather(tmp_path):
         full = torch.from_numpy(oracle.fused_gemm_ref(X.numpy(), W.numpy())).float()
         local = torch.from_numpy(oracle.fused_gemm_ref(pkg.shard_tokens(X, rank, world).numpy(), W.numpy())).float()
         assert torch.equal(pkg.gather_result(local.t().contiguous(), 12, "nm"), full.t())
+        # uneven split (7 tokens over 2 ranks: 4 + 3)
+        inp = oracle.make_inputs("c5", K=64, M=8, N=7)
+        X, W = inp["X"].float(), inp["W"].float()
+        full = torch.from_numpy(oracle.fused_gemm_ref(X.numpy(), W.numpy())).float()
+        local = torch.from_numpy(oracle.fused_gemm_ref(pkg.shard_tokens(X, rank, world).numpy(), W.numpy())).float()
+        assert torch.equal(pkg.gather_result(local, 7, "mn"), full)
         dist.destroy_process_group()
         print("rank", rank, "ok")
     """))
@@ -129,6 +135,39 @@ def test_two_rank_gloo_shard_and_gather(tmp_path):
     r = subprocess.run(
         [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
          "--master-addr", "127.0.0.1", "--master-port", "29617", str(script)],
+        capture_output=True, text=True, env=env, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert r.stdout.count("ok") == 2
+
+
+def test_two_rank_gloo_row_sharded_gemv(tmp_path):
+    """World-size-2 run on CPU for the small-batch split: every rank keeps a block of rows of W, the per-rank result
+    is faked with the oracle, one all-gather assembles Y; uneven and even row counts."""
+    script = tmp_path / "worker.py"
+    script.write_text(textwrap.dedent(f"""
+        import importlib, os, sys
+        sys.path.insert(0, {str(ROOT)!r})
+        import numpy as np, torch, torch.distributed as dist
+        pkg = importlib.import_module("6s894_project_2025_b200")
+        oracle = importlib.import_module("oracle.fwht_oracle")
+        dist.init_process_group("gloo")
+        rank, world = dist.get_rank(), dist.get_world_size()
+        for M, N, B in ((37, 64, 3), (16, 32, 4)):
+            g = torch.Generator().manual_seed(9)
+            W = torch.randn(M, N, generator=g); X = torch.randn(N, B, generator=g)
+            full = torch.from_numpy(oracle.fused_gemv_ref(W.double().numpy(), X.double().numpy())).float()
+            Ws = pkg.shard_rows(W, rank, world)
+            assert Ws.shape[0] == pkg.row_range(M, rank, world)[1] - pkg.row_range(M, rank, world)[0]
+            local = torch.from_numpy(oracle.fused_gemv_ref(Ws.double().numpy(), X.double().numpy())).float()
+            got = pkg.gather_rows(local, M)
+            assert torch.equal(got, full), "row gather differs"
+        dist.destroy_process_group()
+        print("rank", rank, "ok")
+    """))
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="1")
+    r = subprocess.run(
+        [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+         "--master-addr", "127.0.0.1", "--master-port", "29618", str(script)],
         capture_output=True, text=True, env=env, timeout=300)
     assert r.returncode == 0, r.stdout + r.stderr
     assert r.stdout.count("ok") == 2

@@ -42,3 +42,38 @@ def test_two_gpu_token_shards_and_nccl_gather(tmp_path):
          "--master-addr", "127.0.0.1", "--master-port", "29644", str(script)],
         capture_output=True, text=True, env=env, timeout=600)
     assert r.returncode == 0 and r.stdout.count("ok") == 2, r.stdout + r.stderr
+
+
+@pytest.mark.gpu
+def test_two_gpu_row_sharded_gemv(tmp_path):
+    """Small-batch split: each GPU streams half of the rows of W, transforms the same X, and an NCCL all-gather of
+    M x B values assembles Y; the result equals the single-GPU call bit for bit."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    script = tmp_path / "worker.py"
+    script.write_text(textwrap.dedent(f"""
+        import importlib, os, sys
+        sys.path.insert(0, {str(ROOT)!r})
+        import torch, torch.distributed as dist
+        pkg = importlib.import_module("6s894_project_2025_b200")
+        oracle = importlib.import_module("oracle.fwht_oracle")
+        rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"])
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+        for B in (1, 4, 16):
+            inp = oracle.make_inputs("c4", B=B)
+            W, X = inp["W"].cuda(), inp["X"].cuda()
+            full = pkg.fused_ht_gemv(W, X)
+            local = pkg.fused_ht_gemv(pkg.shard_rows(W, rank, world).contiguous(), X)
+            got = pkg.gather_rows(local, W.shape[0])
+            assert torch.equal(got, full), "row-sharded result differs"
+        assert pkg.device_status() == 0
+        dist.barrier(); dist.destroy_process_group()
+        print("rank", rank, "ok")
+    """))
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0")
+    r = subprocess.run(
+        [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+         "--master-addr", "127.0.0.1", "--master-port", "29645", str(script)],
+        capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0 and r.stdout.count("ok") == 2, r.stdout + r.stderr
