@@ -47,7 +47,7 @@ def test_two_gpu_token_shards_and_nccl_gather(tmp_path):
 @pytest.mark.gpu
 def test_two_gpu_row_sharded_gemv(tmp_path):
     """Small-batch split: each GPU streams half of the rows of W, transforms the same X, and an NCCL all-gather of
-    M x B values assembles Y; the result equals the single-GPU call bit for bit."""
+    M x B values assembles Y; the result equals the single-GPU call up to fp32 summation order."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     script = tmp_path / "worker.py"
@@ -66,7 +66,10 @@ def test_two_gpu_row_sharded_gemv(tmp_path):
             full = pkg.fused_ht_gemv(W, X)
             local = pkg.fused_ht_gemv(pkg.shard_rows(W, rank, world).contiguous(), X)
             got = pkg.gather_rows(local, W.shape[0])
-            assert torch.equal(got, full), "row-sharded result differs"
+            # a shard has other rows per CTA than the full matrix, hence another split of K over the warps and
+            # another order of the fp32 partial sums: equal up to fp32 rounding, not bit for bit
+            err = float((got - full).norm() / full.norm())
+            assert err < 1e-5, f"row-sharded result differs: {{err}}"
         assert pkg.device_status() == 0
         dist.barrier(); dist.destroy_process_group()
         print("rank", rank, "ok")
