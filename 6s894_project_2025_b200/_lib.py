@@ -26,6 +26,7 @@ EXPORTS = (
     "b200ht_fused_gemm_tc_workspace_bytes",
     "b200ht_fused_gemm",
     "b200ht_fused_gemm_signed",
+    "b200ht_fused_gemm_scaled",
     "b200ht_fused_gemm_static",
     "b200ht_fused_gemv",
     "b200ht_device_status",
@@ -49,6 +50,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.b200ht_fwht_signed.argtypes = [vp, vp, ctypes.c_uint64, ctypes.c_uint32, i, f, vp, vp]
     lib.b200ht_fused_gemm_signed.restype = i
     lib.b200ht_fused_gemm_signed.argtypes = [vp, vp, vp, i, i, i, i, i, i, f, vp, vp, ctypes.c_size_t, vp]
+    lib.b200ht_fused_gemm_scaled.restype = i
+    lib.b200ht_fused_gemm_scaled.argtypes = [vp, vp, vp, i, i, i, i, i, i, f, vp, vp, vp, vp, ctypes.c_size_t, vp]
     lib.b200ht_fused_gemm_workspace_bytes.restype = ctypes.c_size_t
     lib.b200ht_fused_gemm_workspace_bytes.argtypes = [i, i, i, i]
     lib.b200ht_fused_gemm_tc_workspace_bytes.restype = ctypes.c_size_t

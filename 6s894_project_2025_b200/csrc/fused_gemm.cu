@@ -15,7 +15,8 @@ int launch_fwht_f32_split(const float *in, __nv_bfloat16 *split, uint64_t rows, 
 int launch_fwht(const void *in, void *out, uint64_t rows, uint32_t n, int dtype, float scale, const void *signs,
                 cudaStream_t st);
 int launch_gemm_bf16_tcgen05(const void *Y, const void *W, void *C, int M, int N, int K, int out_dtype,
-                             int out_layout, cudaStream_t st);
+                             int out_layout, cudaStream_t st, const float *row_scale = nullptr,
+                             const float *tok_scale = nullptr);
 
 // ---------------------------------------------------------------------------
 // C[m, n] = sum_k A[m, k] * Bm[n, k]   (both operands K-contiguous), fp32 FFMA.
@@ -145,6 +146,20 @@ static int launch_sgemm(const float *A, const float *Bm, void *C, int M, int N, 
     return (int)cudaGetLastError();
 }
 
+// Epilogue scales for the FFMA path (correctness cases): C[m, t] *= row_scale[m] * tok_scale[t], one pass over C.
+__global__ void __launch_bounds__(256) scale_c_kernel(void *C, int M, int N, int out_dtype, int out_layout,
+                                                      const float *row_scale, const float *tok_scale)
+{
+    const size_t total = (size_t)M * N;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int m = out_layout == B200HT_OUT_MN ? (int)(i / N) : (int)(i % M);
+        const int t = out_layout == B200HT_OUT_MN ? (int)(i % N) : (int)(i / M);
+        const float f = (row_scale ? row_scale[m] : 1.f) * (tok_scale ? tok_scale[t] : 1.f);
+        if (out_dtype == B200HT_F32) ((float *)C)[i] *= f;
+        else ((__nv_bfloat16 *)C)[i] = __float2bfloat16_rn(__bfloat162float(((__nv_bfloat16 *)C)[i]) * f);
+    }
+}
+
 // ---------------------------------------------------------------------------
 // fp32 on the tensor cores: every fp32 operand is the exact sum of three bf16
 // terms (8 + 8 + 8 significant bits), a = a1 + a2 + a3.  Of the nine cross
@@ -203,7 +218,8 @@ static bool fp32_tc_shape(int M, int N, int K) { return K >= 32 && K <= 4096 && 
 // X (fp32, untransformed) and W (fp32) -> C through the split contraction; `ws` is the part of the workspace behind
 // the fp32 H(X) area (which this path leaves unused: the transform kernel writes the split rows directly).
 static int launch_fp32_tc(const float *X, const float *W, void *C, int M, int N, int K, float scale, int out_dtype,
-                          int out_layout, unsigned char *ws, cudaStream_t st)
+                          int out_layout, unsigned char *ws, cudaStream_t st, const float *row_scale,
+                          const float *tok_scale)
 {
     __nv_bfloat16 *Ws = (__nv_bfloat16 *)ws;
     __nv_bfloat16 *Ys = (__nv_bfloat16 *)(ws + ((((size_t)M * K * 12) + 255) & ~(size_t)255));
@@ -216,7 +232,7 @@ static int launch_fp32_tc(const float *X, const float *W, void *C, int M, int N,
         (const float4 *)W, Ws, wv, K, 1);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
-    return launch_gemm_bf16_tcgen05(Ys, Ws, C, M, N, 6 * K, out_dtype, out_layout, st);
+    return launch_gemm_bf16_tcgen05(Ys, Ws, C, M, N, 6 * K, out_dtype, out_layout, st, row_scale, tok_scale);
 }
 
 }  // namespace b200ht
@@ -240,7 +256,7 @@ extern "C" size_t b200ht_fused_gemm_workspace_bytes(int M, int N, int K, int in_
 
 static int fused_gemm_entry(const void *X, const void *W, void *C, int M, int N, int K, int in_dtype, int out_dtype,
                             int out_layout, float scale, const void *signs, void *workspace, size_t workspace_bytes,
-                            void *stream)
+                            void *stream, const float *row_scale = nullptr, const float *tok_scale = nullptr)
 {
     using namespace b200ht;
     if (in_dtype != B200HT_F32 && in_dtype != B200HT_BF16) return B200HT_ERR_DTYPE;
@@ -262,12 +278,20 @@ static int fused_gemm_entry(const void *X, const void *W, void *C, int M, int N,
     // contraction, the minimal one the exact FFMA kernel
     if (in_dtype == B200HT_F32 && fp32_tc_shape(M, N, K) && workspace_bytes >= fp32_tc_workspace_bytes(M, N, K))
         return launch_fp32_tc((const float *)X, (const float *)W, C, M, N, K, scale, out_dtype, out_layout,
-                              (unsigned char *)workspace + ((((size_t)N * K * 4) + 255) & ~(size_t)255), st);
+                              (unsigned char *)workspace + ((((size_t)N * K * 4) + 255) & ~(size_t)255), st, row_scale,
+                              tok_scale);
     rc = launch_fwht(X, workspace, (uint64_t)N, (uint32_t)K, in_dtype, scale, signs, st);
     if (rc) return rc;
-    if (in_dtype == B200HT_F32)
-        return launch_sgemm((const float *)W, (const float *)workspace, C, M, N, K, out_dtype, out_layout, st);
-    return launch_gemm_bf16_tcgen05(workspace, W, C, M, N, K, out_dtype, out_layout, st);
+    if (in_dtype == B200HT_F32) {
+        rc = launch_sgemm((const float *)W, (const float *)workspace, C, M, N, K, out_dtype, out_layout, st);
+        if (rc || (!row_scale && !tok_scale)) return rc;
+        const size_t total = (size_t)M * N;
+        const unsigned grid = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+        note_launch();
+        scale_c_kernel<<<grid, 256, 0, st>>>(C, M, N, out_dtype, out_layout, row_scale, tok_scale);
+        return (int)cudaGetLastError();
+    }
+    return launch_gemm_bf16_tcgen05(workspace, W, C, M, N, K, out_dtype, out_layout, st, row_scale, tok_scale);
 }
 
 extern "C" int b200ht_fused_gemm(const void *X, const void *W, void *C, int M, int N, int K, int in_dtype,
@@ -285,6 +309,16 @@ extern "C" int b200ht_fused_gemm_signed(const void *X, const void *W, void *C, i
     if (!signs) return B200HT_ERR_NULL;
     return fused_gemm_entry(X, W, C, M, N, K, in_dtype, out_dtype, out_layout, scale, signs, workspace,
                             workspace_bytes, stream);
+}
+
+extern "C" int b200ht_fused_gemm_scaled(const void *X, const void *W, void *C, int M, int N, int K, int in_dtype,
+                                        int out_dtype, int out_layout, float scale, const void *signs,
+                                        const float *row_scale, const float *tok_scale, void *workspace,
+                                        size_t workspace_bytes, void *stream)
+{
+    if ((row_scale && ((uintptr_t)row_scale & 3u)) || (tok_scale && ((uintptr_t)tok_scale & 3u))) return B200HT_ERR_ALIGN;
+    return fused_gemm_entry(X, W, C, M, N, K, in_dtype, out_dtype, out_layout, scale, signs, workspace,
+                            workspace_bytes, stream, row_scale, tok_scale);
 }
 
 // ---------------------------------------------------------------------------

@@ -41,6 +41,22 @@ struct TcCfg {
     static constexpr int THREADS = 64 + 128 * MT;       // TMA warp, MMA warp, 4 * MT epilogue warps
 };
 
+// Optional epilogue scales: C[m, t] is multiplied by row_scale[m] (per output channel) and tok_scale[t] (per token)
+// before the store; `rs` is this lane's row factor (1 when there is none), `n` the token of r[0].
+__device__ __forceinline__ void tc_scale_chunk(uint32_t (&r)[32], float rs, const float *tok_scale, int n, int N)
+{
+    if (tok_scale) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const float ts = n + j < N ? __ldg(tok_scale + n + j) : 0.f;
+            r[j] = __float_as_uint(__uint_as_float(r[j]) * (rs * ts));
+        }
+    } else if (rs != 1.f) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * rs);
+    }
+}
+
 // `ld` is the leading dimension of C in elements (N for M x N, M for N x M, larger when C is a block of a bigger
 // matrix).
 template <int OUT_DT, int LAYOUT>
@@ -108,7 +124,7 @@ template <int OUT_DT, int LAYOUT, int MT>
 __global__ void __launch_bounds__(TcCfg<MT>::THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmY,
                const __grid_constant__ CUtensorMap tmC, int tma_store, void *C, int M, int N, int K, size_t ldc,
-               int ntiles_run, int pdl_mode, int *status)
+               int ntiles_run, int pdl_mode, const float *row_scale, const float *tok_scale, int *status)
 {
     using Cfg = TcCfg<MT>;
     constexpr int STAGES = Cfg::STAGES, STAGE_BYTES = Cfg::STAGE_BYTES, NACC = Cfg::NACC;
@@ -243,6 +259,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             bool released = false;   // set where the accumulator is handed back before the stores
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (acc + h) * TC_BN;
             const int m = m0 + h * 128 + q * 32 + lane;
+            const float rs = row_scale && m < M ? __ldg(row_scale + m) : 1.f;
             if (LAYOUT == B200HT_OUT_MN && tma_store) {
                 // M x N layout: a lane owns a row, so plain stores would scatter 16-byte pieces over 32 rows.
                 // Stage 32 rows x 128 bytes per warp in shared memory (128-byte swizzle) and let TMA write them.
@@ -256,6 +273,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     tmem_ld32(taddr + c, r);
                     if (OUT_DT != B200HT_F32) tmem_ld32(taddr + c + 32, r2);
                     tmem_ld_wait();
+                    tc_scale_chunk(r, rs, tok_scale, n0 + c, N);
+                    if (OUT_DT != B200HT_F32) tc_scale_chunk(r2, rs, tok_scale, n0 + c + 32, N);
                     // the buffer about to be overwritten must have been read by its previous store
                     if (lane == 0) {
                         if (Cfg::STORE_BUFS == 2) asm volatile("cp.async.bulk.wait_group.read 1;\n" ::: "memory");
@@ -305,6 +324,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     uint32_t r[32];
                     tmem_ld32(taddr + cc * 32, r);
                     tmem_ld_wait();
+                    tc_scale_chunk(r, rs, tok_scale, n0 + cc * 32, N);
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
                         pk[cc * 16 + j] = pack2<B200HT_BF16>(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
@@ -337,6 +357,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     uint32_t r[32];
                     tmem_ld32(taddr + c, r);
                     tmem_ld_wait();
+                    tc_scale_chunk(r, rs, tok_scale, n0 + c, N);
                     tc_store_chunk<OUT_DT, LAYOUT>(C, M, N, ldc, m, n0 + c, r);
                 }
             }
@@ -363,7 +384,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 // K < 64 (the 128-byte swizzled tile needs 64 bf16 per row): plain SIMT kernel.
 // ---------------------------------------------------------------------------
 __global__ void gemm_bf16_smallk_kernel(const __nv_bfloat16 *Y, const __nv_bfloat16 *W, void *C, int M, int N,
-                                        int K, int out_dtype, int out_layout)
+                                        int K, int out_dtype, int out_layout, const float *row_scale,
+                                        const float *tok_scale)
 {
     const int n = blockIdx.x * blockDim.x + threadIdx.x;
     const int m = blockIdx.y * blockDim.y + threadIdx.y;
@@ -371,6 +393,8 @@ __global__ void gemm_bf16_smallk_kernel(const __nv_bfloat16 *Y, const __nv_bfloa
     float acc = 0.f;
     for (int k = 0; k < K; ++k)
         acc = fmaf(__bfloat162float(W[(size_t)m * K + k]), __bfloat162float(Y[(size_t)n * K + k]), acc);
+    if (row_scale) acc *= row_scale[m];
+    if (tok_scale) acc *= tok_scale[n];
     const size_t idx = out_layout == B200HT_OUT_MN ? (size_t)m * N + n : (size_t)n * M + m;
     if (out_dtype == B200HT_F32) ((float *)C)[idx] = acc;
     else ((__nv_bfloat16 *)C)[idx] = __float2bfloat16_rn(acc);
@@ -463,7 +487,7 @@ static int sm_count_tc()
 
 template <int OUT_DT, int LAYOUT, int MT>
 static int launch_tc_mt(const void *Y, const void *W, void *C, int M, int N, int K, size_t ldc, int skip_last_tiles,
-                        int pdl_mode, cudaStream_t st)
+                        int pdl_mode, const float *row_scale, const float *tok_scale, cudaStream_t st)
 {
     using Cfg = TcCfg<MT>;
     CUtensorMap tw, ty;
@@ -486,11 +510,12 @@ static int launch_tc_mt(const void *Y, const void *W, void *C, int M, int N, int
     const int tiles = ((M + Cfg::BM - 1) / Cfg::BM) * ((N + TC_BN - 1) / TC_BN) - skip_last_tiles;
     const int grid = tiles < sm_count_tc() ? tiles : sm_count_tc();
     return launch_pdl(gemm_tc_kernel<OUT_DT, LAYOUT, MT>, dim3(grid), dim3(Cfg::THREADS), (size_t)Cfg::SMEM_BYTES, st,
-                      tw, ty, tc, tma_store, C, M, N, K, ldc, tiles, pdl_mode, status_word_ptr());
+                      tw, ty, tc, tma_store, C, M, N, K, ldc, tiles, pdl_mode, row_scale, tok_scale, status_word_ptr());
 }
 
 template <int OUT_DT, int LAYOUT>
-static int launch_tc(const void *Y, const void *W, void *C, int M, int N, int K, cudaStream_t st)
+static int launch_tc(const void *Y, const void *W, void *C, int M, int N, int K, const float *row_scale,
+                     const float *tok_scale, cudaStream_t st)
 {
     // 256-row or 128-row CTA tiles: whichever needs less time in units of a 128-row tile, counting whole waves
     // over the SMs (a 256-row tile costs two units; 128-row tiles pay about 3 % more for operand traffic).
@@ -518,39 +543,42 @@ static int launch_tc(const void *Y, const void *W, void *C, int M, int N, int K,
     const double cost128 = 1.03 * (double)((tiles128 + sms - 1) / sms);
     const double cost256 = can_split ? 2.0 * (double)(tiles256 / sms) + 1.03 : 2.0 * (double)((tiles256 + sms - 1) / sms);
     const bool big = force_mt ? force_mt == 2 : (tiles256 >= sms && cost256 <= cost128);
-    if (!big) return launch_tc_mt<OUT_DT, LAYOUT, 1>(Y, W, C, M, N, K, ldc, 0, 0, st);
+    if (!big) return launch_tc_mt<OUT_DT, LAYOUT, 1>(Y, W, C, M, N, K, ldc, 0, 0, row_scale, tok_scale, st);
     if (can_split && !force_mt) {
         const long cols = rem <= gl ? 1 : rem / gl;          // token blocks of the rectangle
         const long rows = rem <= gl ? rem : gl;              // 256-row blocks of the rectangle
         const long row_off = (mt256 - rows) * 256, tok_off = (nt - cols) * TC_BN;
-        int rc = launch_tc_mt<OUT_DT, LAYOUT, 2>(Y, W, C, M, N, K, ldc, (int)rem, 1, st);
+        int rc = launch_tc_mt<OUT_DT, LAYOUT, 2>(Y, W, C, M, N, K, ldc, (int)rem, 1, row_scale, tok_scale, st);
         if (rc) return rc;
         const size_t esz = OUT_DT == B200HT_F32 ? 4 : 2;
         const size_t coff = LAYOUT == B200HT_OUT_MN ? (size_t)row_off * ldc + (size_t)tok_off : (size_t)tok_off * ldc + (size_t)row_off;
         return launch_tc_mt<OUT_DT, LAYOUT, 1>((const unsigned char *)Y + (size_t)tok_off * K * 2,
                                                (const unsigned char *)W + (size_t)row_off * K * 2,
                                                (unsigned char *)C + coff * esz, (int)(M - row_off), (int)(N - tok_off), K, ldc,
-                                               0, 2, st);
+                                               0, 2, row_scale ? row_scale + row_off : nullptr,
+                                               tok_scale ? tok_scale + tok_off : nullptr, st);
     }
-    return launch_tc_mt<OUT_DT, LAYOUT, 2>(Y, W, C, M, N, K, ldc, 0, 0, st);
+    return launch_tc_mt<OUT_DT, LAYOUT, 2>(Y, W, C, M, N, K, ldc, 0, 0, row_scale, tok_scale, st);
 }
 
 int launch_gemm_bf16_tcgen05(const void *Y, const void *W, void *C, int M, int N, int K, int out_dtype,
-                             int out_layout, cudaStream_t st)
+                             int out_layout, cudaStream_t st, const float *row_scale, const float *tok_scale)
 {
     if (K < TC_BK) {
         dim3 blk(32, 8), grd((N + 31) / 32, (M + 7) / 8);
         note_launch();
         gemm_bf16_smallk_kernel<<<grd, blk, 0, st>>>((const __nv_bfloat16 *)Y, (const __nv_bfloat16 *)W, C, M, N, K,
-                                                     out_dtype, out_layout);
+                                                     out_dtype, out_layout, row_scale, tok_scale);
         return (int)cudaGetLastError();
     }
     if (out_dtype == B200HT_F32) {
-        return out_layout == B200HT_OUT_MN ? launch_tc<B200HT_F32, B200HT_OUT_MN>(Y, W, C, M, N, K, st)
-                                           : launch_tc<B200HT_F32, B200HT_OUT_NM>(Y, W, C, M, N, K, st);
+        return out_layout == B200HT_OUT_MN
+                   ? launch_tc<B200HT_F32, B200HT_OUT_MN>(Y, W, C, M, N, K, row_scale, tok_scale, st)
+                   : launch_tc<B200HT_F32, B200HT_OUT_NM>(Y, W, C, M, N, K, row_scale, tok_scale, st);
     }
-    return out_layout == B200HT_OUT_MN ? launch_tc<B200HT_BF16, B200HT_OUT_MN>(Y, W, C, M, N, K, st)
-                                       : launch_tc<B200HT_BF16, B200HT_OUT_NM>(Y, W, C, M, N, K, st);
+    return out_layout == B200HT_OUT_MN
+               ? launch_tc<B200HT_BF16, B200HT_OUT_MN>(Y, W, C, M, N, K, row_scale, tok_scale, st)
+               : launch_tc<B200HT_BF16, B200HT_OUT_NM>(Y, W, C, M, N, K, row_scale, tok_scale, st);
 }
 
 }  // namespace b200ht

@@ -102,7 +102,8 @@ def fused_gemm_workspace_bytes(M: int, N: int, K: int, dtype: torch.dtype, exact
 def fused_ht_gemm(X: torch.Tensor, W: torch.Tensor, *, scale: float | None = None,
                   out_dtype: torch.dtype | None = None, out_layout: str = "mn",
                   out: torch.Tensor | None = None, workspace: torch.Tensor | None = None,
-                  signs: torch.Tensor | None = None, exact: bool = False) -> torch.Tensor:
+                  signs: torch.Tensor | None = None, exact: bool = False,
+                  row_scale: torch.Tensor | None = None, token_scale: torch.Tensor | None = None) -> torch.Tensor:
     """C = W . H(X): ``C[m, t] = sum_k W[m, k] * (scale * H_K x_t)[k]``.
 
     ``X`` is (N tokens, K) token-major and ``W`` is (M, K) row-major, the
@@ -116,7 +117,9 @@ def fused_ht_gemm(X: torch.Tensor, W: torch.Tensor, *, scale: float | None = Non
     cores as six bf16 products per fp32 product (relative error up to 4.4e-6
     at K = 4096, about 4x faster than FFMA);
     ``exact=True``, or a caller ``workspace`` of only the minimal size, keeps
-    the FFMA kernel.
+    the FFMA kernel.  ``row_scale`` (M floats, per output channel) and
+    ``token_scale`` (N floats, per token) multiply the fp32 accumulator in the
+    epilogue, before the one rounding of the store.
     """
     if X.dtype != W.dtype or X.dtype not in (torch.float32, torch.bfloat16):
         raise RuntimeError("fused_ht_gemm: X and W must both be float32 or both bfloat16")
@@ -153,7 +156,22 @@ def fused_ht_gemm(X: torch.Tensor, W: torch.Tensor, *, scale: float | None = Non
         with torch.cuda.device(X.device):
             layout = _lib.OUT_MN if out_layout == "mn" else _lib.OUT_NM
             wsb = need if exact else workspace.numel() * workspace.element_size()
-            if signs is None:
+            if row_scale is not None or token_scale is not None:
+                def _vec(v, n, what):
+                    if v is None:
+                        return None
+                    if v.dim() != 1 or int(v.shape[0]) != n:
+                        raise RuntimeError(f"fused_ht_gemm: {what} must be a vector of length {n}")
+                    return v.to(device=X.device, dtype=torch.float32).contiguous()
+                rs, ts = _vec(row_scale, M, "row_scale"), _vec(token_scale, N, "token_scale")
+                mask = sign_mask(signs, K, X.device) if signs is not None else None
+                rc = lib.b200ht_fused_gemm_scaled(X.data_ptr(), W.data_ptr(), out.data_ptr(), M, N, K, _DT[X.dtype],
+                                                  _DT[out_dtype], layout, float(scale),
+                                                  mask.data_ptr() if mask is not None else None,
+                                                  rs.data_ptr() if rs is not None else None,
+                                                  ts.data_ptr() if ts is not None else None,
+                                                  workspace.data_ptr(), wsb, _stream_ptr(X.device))
+            elif signs is None:
                 rc = lib.b200ht_fused_gemm(X.data_ptr(), W.data_ptr(), out.data_ptr(), M, N, K, _DT[X.dtype],
                                            _DT[out_dtype], layout, float(scale), workspace.data_ptr(), wsb,
                                            _stream_ptr(X.device))

@@ -116,6 +116,16 @@ int b200ht_fused_gemm_signed(const void *X, const void *W, void *C, int M, int N
                              const void *signs, void *workspace, size_t workspace_bytes,
                              void *stream);
 
+/* b200ht_fused_gemm with epilogue scales, the cast step of a quantised linear layer:
+ *   C[m, t] = row_scale[m] * tok_scale[t] * sum_k W[m, k] * (scale * H_K (d * x_t))[k]
+ * row_scale (M floats, per output channel), tok_scale (N floats, per token) and signs (as in
+ * b200ht_fused_gemm_signed, BF16 only) may each be NULL.  The factors are applied to the fp32
+ * accumulator before the single rounding of the store.  No counterpart in the reference. */
+int b200ht_fused_gemm_scaled(const void *X, const void *W, void *C, int M, int N, int K,
+                             int in_dtype, int out_dtype, int out_layout, float scale,
+                             const void *signs, const float *row_scale, const float *tok_scale,
+                             void *workspace, size_t workspace_bytes, void *stream);
+
 /*
  * b200ht_fused_gemm without a caller-provided workspace and without any
  * allocation.  No counterpart in the reference (its program allocates all its

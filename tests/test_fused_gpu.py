@@ -291,3 +291,36 @@ def test_fp32_long_rows_keep_the_ffma_kernel(pkg):
         lib.b200ht_fused_gemm_workspace_bytes(64, 64, 64, pkg._lib.F32)
     assert lib.b200ht_fused_gemm_tc_workspace_bytes(4096, 4096, 1024, pkg._lib.BF16) == \
         lib.b200ht_fused_gemm_workspace_bytes(4096, 4096, 1024, pkg._lib.BF16)
+
+
+@pytest.mark.parametrize("dtype,M,N,K", [(torch.bfloat16, 300, 200, 256), (torch.bfloat16, 4096, 2560, 64),
+                                         (torch.bfloat16, 640, 777, 32), (torch.float32, 130, 67, 128),
+                                         (torch.float32, 1024, 768, 1024)])
+def test_epilogue_scales(pkg, oracle, dtype, M, N, K):
+    """Per-channel and per-token factors in the epilogue (b200ht_fused_gemm_scaled): every store path of the
+    tensor-core kernel (both layouts, both output types, whole and ragged tiles, the two-launch form, K < 64), the
+    FFMA path and the fp32 tensor-core path, each factor alone and both, with and without the sign diagonal."""
+    inp = oracle.make_inputs("c3", K=K, N=N, M=M)
+    X, W = inp["X"].to(dtype), inp["W"].to(dtype)
+    g = torch.Generator().manual_seed(3)
+    rs = torch.rand(M, generator=g) + 0.5
+    ts = torch.rand(N, generator=g) * 2 - 1
+    base = oracle.fused_gemm_ref(X.double().numpy(), W.double().numpy())
+    tol = F32_TOL if dtype == torch.float32 else BF16_TOL
+    Xd, Wd = X.cuda(), W.cuda()
+    for r, t in ((rs, ts), (rs, None), (None, ts)):
+        ref = base * (r.double().numpy()[:, None] if r is not None else 1.0) * (t.double().numpy()[None, :] if t is not None else 1.0)
+        for layout in ("mn", "nm"):
+            for od in (torch.float32, torch.bfloat16):
+                C = pkg.fused_ht_gemm(Xd, Wd, out_layout=layout, out_dtype=od, row_scale=r, token_scale=t)
+                got = C.float().cpu().numpy()
+                _check(oracle, got if layout == "mn" else got.T, ref, tol if od == torch.float32 else max(tol, 1e-2))
+    if dtype == torch.bfloat16:
+        d = torch.where(torch.rand(K, generator=g) < 0.5, -1.0, 1.0)
+        ref = oracle.fused_gemm_ref((X.double() * d.double()).numpy(), W.double().numpy()) * rs.double().numpy()[:, None]
+        C = pkg.fused_ht_gemm(Xd, Wd, signs=d, row_scale=rs)
+        _check(oracle, C.cpu().numpy(), ref, tol)
+    else:
+        Ce = pkg.fused_ht_gemm(Xd, Wd, exact=True, row_scale=rs, token_scale=ts)
+        _check(oracle, Ce.cpu().numpy(), base * rs.double().numpy()[:, None] * ts.double().numpy()[None, :], tol)
+    assert pkg.device_status() == 0
