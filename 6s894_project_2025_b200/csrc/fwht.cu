@@ -158,6 +158,10 @@ __global__ void __launch_bounds__(SmemCfg<LOGN>::NW * 32) fwht_smem_kernel(const
     make_hfrag<DT>(A2, lane, 15u, 0.25f);
 
     constexpr int U = 8;   // chunks (16-byte loads per lane) in flight per warp: 8 is 3-5 % faster than 4
+    // Chunks of a missing second row (n = 4096, odd row count) are zeroed: pass 2 multiplies them by the zero entries
+    // of its constant, and 0 * (stale NaN) would poison row one.  (A separate loop: with a compile-time bound on the
+    // main loop the compiler gives up the stage-wise order of rot8x and the kernel loses a fifth of its speed.)
+    for (int c = chunks_here + warp; c < Cfg::NCHUNK; c += NW) sm[c * 33 + lane] = make_uint4(0, 0, 0, 0);
     for (int c0 = warp; c0 < chunks_here; c0 += NW * U) {
         uint4 v[U];
 #pragma unroll

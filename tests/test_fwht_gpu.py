@@ -214,3 +214,18 @@ def test_more_than_2_31_elements(pkg, oracle, n):
     assert float(err.max()) <= 5e-2, float(err.max())
     del x, row_sums
     torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_odd_row_count_after_nan_data_at_4096(pkg, oracle, dtype):
+    """n = 4096 runs two rows per shared-memory slab.  With an odd row count the second half of the last slab holds
+    whatever the previous kernel left there; the kernel must zero it, because its second pass multiplies those
+    chunks by zero and 0 * NaN is NaN.  A transform of NaN data first leaves NaN in the shared memory of every SM."""
+    poison = torch.full((8192, 4096), float("nan"), dtype=dtype, device="cuda")
+    pkg.hadamard_transform(poison, inplace=True)
+    g = torch.Generator().manual_seed(12)
+    for rows in (1, 3, 301):
+        x = torch.randn(rows, 4096, generator=g).to(dtype)
+        y = pkg.hadamard_transform(x.cuda()).double().cpu().numpy()
+        assert np.isfinite(y).all(), rows
+        assert np.max(np.abs(y - _ref(oracle, x))) <= 5e-2
