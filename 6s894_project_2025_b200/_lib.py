@@ -1,7 +1,7 @@
 """ctypes binding of libb200ht.so (the C ABI declared in include/b200ht.h).
 
-There is no CPU fallback: if the shared library is missing it is built with
-nvcc, and if that is impossible the import of an op raises.
+There is no CPU fallback: if the shared library is missing or stale it is built
+with nvcc, and if that is impossible the import of an op raises.
 """
 from __future__ import annotations
 
@@ -71,17 +71,22 @@ def _declare(lib: ctypes.CDLL) -> None:
 
 
 def load(build_if_missing: bool = True) -> ctypes.CDLL:
-    """Load (building first if needed) the shared library; raises if impossible."""
+    """Load the shared library; raises if impossible.
+
+    The library is (re)built first when it is missing or was built from other sources than the ones on disk (a
+    digest of sources, headers and flags is stored beside it), so a stale binary is never loaded against a newer
+    header.  The build takes a file lock: ranks started together do not compile the same objects twice.
+    """
     global _lib
     with _lock:
         if _lib is not None:
             return _lib
-        if not LIB_PATH.exists():
-            if not build_if_missing:
-                raise RuntimeError(f"{LIB_PATH} is missing and there is no fallback implementation")
-            from .build import build
+        from . import build as _build
 
-            build()
+        if not _build.is_current():
+            if not build_if_missing:
+                raise RuntimeError(f"{LIB_PATH} is missing or stale and there is no fallback implementation")
+            _build.build()
         lib = ctypes.CDLL(str(LIB_PATH))
         for name in EXPORTS:
             if not hasattr(lib, name):

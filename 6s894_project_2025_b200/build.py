@@ -22,6 +22,7 @@ CSRC = HERE / "csrc"
 ROOT = HERE.parent
 OUT = HERE / "libb200ht.so"
 OBJ_DIR = HERE / "build"
+STAMP = HERE / "libb200ht.so.sha"   # digest of the sources the library was built from
 
 SOURCES = ["api.cu", "fwht.cu", "fwht_tcgen05.cu", "fused_gemm.cu", "gemm_tcgen05.cu", "fused_gemv.cu"]
 
@@ -30,11 +31,8 @@ NVCC_FLAGS = [
     "-O3", "-std=c++17", "-lineinfo",
     "-Xcompiler", "-fPIC",
     "--expt-relaxed-constexpr",
-    *(["-DB200HT_GEMV_TRACE"] if os.environ.get("B200HT_GEMV_TRACE") else []),  # developer timing hooks
-    *(["-DB200HT_FWHT_TRACE"] if os.environ.get("B200HT_FWHT_TRACE") else []),
-    *os.environ.get("B200HT_NVCC_EXTRA", "").split(),  # developer experiments
-    "-I", str(ROOT / "include"),
 ]
+INCLUDE_FLAGS = ["-I", str(ROOT / "include")]   # not part of the digest: the checkout may sit at any path
 
 
 def find_nvcc() -> str:
@@ -53,41 +51,58 @@ def _digest(paths) -> str:
     return h.hexdigest()
 
 
+def source_digest() -> str:
+    """Digest of everything libb200ht.so is built from (sources, headers, flags)."""
+    return _digest([CSRC / s for s in SOURCES] + list(CSRC.glob("*.cuh")) + [ROOT / "include" / "b200ht.h"])
+
+
+def is_current() -> bool:
+    """True when libb200ht.so exists and was built from the sources as they are now."""
+    return OUT.exists() and STAMP.exists() and STAMP.read_text().strip() == source_digest()
+
+
 def build(verbose: bool = False, force: bool = False) -> Path:
+    """Compile what changed and link.  Safe to call from several processes at once (one builds, the others wait)."""
+    import fcntl
+
     nvcc = find_nvcc()
     OBJ_DIR.mkdir(exist_ok=True)
-    headers = list(CSRC.glob("*.cuh")) + [ROOT / "include" / "b200ht.h"]
-    jobs = []
-    objs = []
-    for src in SOURCES:
-        s = CSRC / src
-        o = OBJ_DIR / (s.stem + ".o")
-        stamp = OBJ_DIR / (s.stem + ".sha")
-        dig = _digest([s] + headers)
-        objs.append(o)
-        if force or not o.exists() or not stamp.exists() or stamp.read_text() != dig:
-            cmd = [nvcc, *NVCC_FLAGS, "-c", str(s), "-o", str(o)]
+    with open(HERE / ".build.lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        if not force and is_current():
+            return OUT
+        headers = list(CSRC.glob("*.cuh")) + [ROOT / "include" / "b200ht.h"]
+        jobs = []
+        objs = []
+        for src in SOURCES:
+            s = CSRC / src
+            o = OBJ_DIR / (s.stem + ".o")
+            stamp = OBJ_DIR / (s.stem + ".sha")
+            dig = _digest([s] + headers)
+            objs.append(o)
+            if force or not o.exists() or not stamp.exists() or stamp.read_text() != dig:
+                cmd = [nvcc, *NVCC_FLAGS, *INCLUDE_FLAGS, "-c", str(s), "-o", str(o)]
+                if verbose:
+                    cmd.insert(1, "-Xptxas=-v")
+                jobs.append((cmd, stamp, dig))
+
+        def run(job):
+            cmd, stamp, dig = job
+            r = subprocess.run(cmd, capture_output=True, text=True)
+            if r.returncode != 0:
+                raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + r.stdout + r.stderr)
             if verbose:
-                cmd.insert(1, "-Xptxas=-v")
-            jobs.append((cmd, stamp, dig))
+                sys.stderr.write(r.stderr)
+            stamp.write_text(dig)
 
-    def run(job):
-        cmd, stamp, dig = job
-        r = subprocess.run(cmd, capture_output=True, text=True)
-        if r.returncode != 0:
-            raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + r.stdout + r.stderr)
-        if verbose:
-            sys.stderr.write(r.stderr)
-        stamp.write_text(dig)
-
-    if jobs:
-        with ThreadPoolExecutor(max_workers=min(len(jobs), os.cpu_count() or 4)) as ex:
-            list(ex.map(run, jobs))
-    if jobs or not OUT.exists():
+        if jobs:
+            with ThreadPoolExecutor(max_workers=min(len(jobs), os.cpu_count() or 4)) as ex:
+                list(ex.map(run, jobs))
         cmd = [nvcc, "-shared", "-o", str(OUT), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("link failed:\n" + r.stdout + r.stderr)
+        STAMP.write_text(source_digest())
     return OUT
 
 

@@ -11,29 +11,88 @@ __device__ int g_status_word = 0;
 static std::atomic<unsigned long long> g_launches{0};
 void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
-int *status_word_ptr()
-{
-    int *p = nullptr;
-    if (cudaGetSymbolAddress((void **)&p, g_status_word) != cudaSuccess) return nullptr;
-    return p;
-}
+// Per-device facts resolved once (mutex-guarded), then read without a lock: architecture check, SM count and the
+// device address of the status word.  Every launcher needs them on every call, and each costs a runtime query.
+struct DeviceFacts {
+    std::atomic<int> state{0};   // 0 unknown, 1 sm_100, 2 other architecture
+    int sms = 148;
+    int *status = nullptr;
+};
+static DeviceFacts g_dev[64];
+static std::mutex g_dev_mu;
 
-int check_device()
+static int device_facts(const DeviceFacts **out)
 {
-    static std::mutex mu;
-    static int ok_mask[64] = {0};  // 0 unknown, 1 ok, 2 wrong architecture
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
     if (dev < 0 || dev >= 64) return B200HT_ERR_DEVICE;
-    std::lock_guard<std::mutex> lk(mu);
-    if (ok_mask[dev] == 0) {
-        int major = 0;
-        e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
-        if (e != cudaSuccess) return (int)e;
-        ok_mask[dev] = (major == 10) ? 1 : 2;
+    DeviceFacts &f = g_dev[dev];
+    if (f.state.load(std::memory_order_acquire) == 0) {
+        std::lock_guard<std::mutex> lk(g_dev_mu);
+        if (f.state.load(std::memory_order_relaxed) == 0) {
+            int major = 0, sms = 148;
+            e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+            if (e != cudaSuccess) return (int)e;
+            if (major == 10) {
+                e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+                if (e != cudaSuccess) return (int)e;
+                int *p = nullptr;
+                e = cudaGetSymbolAddress((void **)&p, g_status_word);
+                if (e != cudaSuccess) return (int)e;
+                f.sms = sms;
+                f.status = p;
+            }
+            f.state.store(major == 10 ? 1 : 2, std::memory_order_release);
+        }
     }
-    return ok_mask[dev] == 1 ? 0 : B200HT_ERR_DEVICE;
+    *out = &f;
+    return 0;
+}
+
+int *status_word_ptr()
+{
+    const DeviceFacts *f = nullptr;
+    if (device_facts(&f) != 0 || f->state.load(std::memory_order_relaxed) != 1) return nullptr;
+    return f->status;
+}
+
+int sm_count()
+{
+    const DeviceFacts *f = nullptr;
+    if (device_facts(&f) != 0) return 148;
+    return f->sms;
+}
+
+int check_device()
+{
+    const DeviceFacts *f = nullptr;
+    const int rc = device_facts(&f);
+    if (rc) return rc;
+    return f->state.load(std::memory_order_relaxed) == 1 ? 0 : B200HT_ERR_DEVICE;
+}
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (device, kernel) and size: repeated calls with a size
+// that is already granted return at once.
+int ensure_dyn_smem(const void *func, int bytes)
+{
+    struct Entry { const void *func; int dev; int bytes; };
+    static std::mutex mu;
+    static Entry table[256];
+    static int used = 0;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    std::lock_guard<std::mutex> lk(mu);
+    Entry *slot = nullptr;
+    for (int i = 0; i < used; ++i)
+        if (table[i].func == func && table[i].dev == dev) { slot = &table[i]; break; }
+    if (slot && slot->bytes >= bytes) return 0;
+    e = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return (int)e;
+    if (!slot && used < 256) slot = &table[used++];
+    if (slot) { slot->func = func; slot->dev = dev; slot->bytes = bytes; }
+    return 0;
 }
 
 }  // namespace b200ht

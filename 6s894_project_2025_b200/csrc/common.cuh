@@ -34,6 +34,11 @@ int *status_word_ptr();  // device address of the status word on the current dev
 
 // Checks (once per device) that the current device is compute capability 10.x.
 int check_device();
+// Number of SMs of the current device (cached per device).
+int sm_count();
+// Raises the dynamic shared-memory limit of `func` to `bytes` on the current device; the runtime is asked only when
+// the cached limit is lower.
+int ensure_dyn_smem(const void *func, int bytes);
 
 // Launch with programmatic stream serialization (programmatic dependent launch): the
 // kernel may be scheduled while its predecessor in the stream is still draining.  Every

@@ -44,7 +44,8 @@ __device__ __forceinline__ float4 sg_load4(const float *base, int row, int nrows
 
 template <int OUT_DT, int LAYOUT>
 __global__ void __launch_bounds__(256)
-sgemm_nt_kernel(const float *A, const float *Bm, void *C, int M, int N, int K, int vec)
+sgemm_nt_kernel(const float *A, const float *Bm, void *C, int M, int N, int K, int vec, const float *row_scale,
+                const float *tok_scale)
 {
     __shared__ __align__(16) float As[2][SG_BK][SG_BM + SG_PAD];
     __shared__ __align__(16) float Bs[2][SG_BK][SG_BN + SG_PAD];
@@ -106,6 +107,15 @@ sgemm_nt_kernel(const float *A, const float *Bm, void *C, int M, int N, int K, i
     for (int i = 0; i < 8; ++i) {
         const int m = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
         if (m >= M) continue;
+        // optional epilogue scales, applied to the fp32 sums before the one rounding of the store
+        if (row_scale || tok_scale) {
+            const float rs = row_scale ? row_scale[m] : 1.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int n = n0 + (j >> 2) * 64 + tx * 4 + (j & 3);
+                acc[i][j] *= rs * (tok_scale && n < N ? tok_scale[n] : 1.f);
+            }
+        }
 #pragma unroll
         for (int jh = 0; jh < 2; ++jh) {
             const int n = n0 + jh * 64 + tx * 4;
@@ -127,37 +137,23 @@ sgemm_nt_kernel(const float *A, const float *Bm, void *C, int M, int N, int K, i
 }
 
 static int launch_sgemm(const float *A, const float *Bm, void *C, int M, int N, int K, int out_dtype,
-                        int out_layout, cudaStream_t st)
+                        int out_layout, cudaStream_t st, const float *row_scale, const float *tok_scale)
 {
     dim3 grid((N + SG_BN - 1) / SG_BN, (M + SG_BM - 1) / SG_BM);
     const int vec = ((K & 3) == 0 && aligned16(A) && aligned16(Bm)) ? 1 : 0;
     note_launch();
     if (out_dtype == B200HT_F32) {
         if (out_layout == B200HT_OUT_MN)
-            sgemm_nt_kernel<B200HT_F32, B200HT_OUT_MN><<<grid, 256, 0, st>>>(A, Bm, C, M, N, K, vec);
+            sgemm_nt_kernel<B200HT_F32, B200HT_OUT_MN><<<grid, 256, 0, st>>>(A, Bm, C, M, N, K, vec, row_scale, tok_scale);
         else
-            sgemm_nt_kernel<B200HT_F32, B200HT_OUT_NM><<<grid, 256, 0, st>>>(A, Bm, C, M, N, K, vec);
+            sgemm_nt_kernel<B200HT_F32, B200HT_OUT_NM><<<grid, 256, 0, st>>>(A, Bm, C, M, N, K, vec, row_scale, tok_scale);
     } else {
         if (out_layout == B200HT_OUT_MN)
-            sgemm_nt_kernel<B200HT_BF16, B200HT_OUT_MN><<<grid, 256, 0, st>>>(A, Bm, C, M, N, K, vec);
+            sgemm_nt_kernel<B200HT_BF16, B200HT_OUT_MN><<<grid, 256, 0, st>>>(A, Bm, C, M, N, K, vec, row_scale, tok_scale);
         else
-            sgemm_nt_kernel<B200HT_BF16, B200HT_OUT_NM><<<grid, 256, 0, st>>>(A, Bm, C, M, N, K, vec);
+            sgemm_nt_kernel<B200HT_BF16, B200HT_OUT_NM><<<grid, 256, 0, st>>>(A, Bm, C, M, N, K, vec, row_scale, tok_scale);
     }
     return (int)cudaGetLastError();
-}
-
-// Epilogue scales for the FFMA path (correctness cases): C[m, t] *= row_scale[m] * tok_scale[t], one pass over C.
-__global__ void __launch_bounds__(256) scale_c_kernel(void *C, int M, int N, int out_dtype, int out_layout,
-                                                      const float *row_scale, const float *tok_scale)
-{
-    const size_t total = (size_t)M * N;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        const int m = out_layout == B200HT_OUT_MN ? (int)(i / N) : (int)(i % M);
-        const int t = out_layout == B200HT_OUT_MN ? (int)(i % N) : (int)(i / M);
-        const float f = (row_scale ? row_scale[m] : 1.f) * (tok_scale ? tok_scale[t] : 1.f);
-        if (out_dtype == B200HT_F32) ((float *)C)[i] *= f;
-        else ((__nv_bfloat16 *)C)[i] = __float2bfloat16_rn(__bfloat162float(((__nv_bfloat16 *)C)[i]) * f);
-    }
 }
 
 // ---------------------------------------------------------------------------
@@ -283,13 +279,8 @@ static int fused_gemm_entry(const void *X, const void *W, void *C, int M, int N,
     rc = launch_fwht(X, workspace, (uint64_t)N, (uint32_t)K, in_dtype, scale, signs, st);
     if (rc) return rc;
     if (in_dtype == B200HT_F32) {
-        rc = launch_sgemm((const float *)W, (const float *)workspace, C, M, N, K, out_dtype, out_layout, st);
-        if (rc || (!row_scale && !tok_scale)) return rc;
-        const size_t total = (size_t)M * N;
-        const unsigned grid = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-        note_launch();
-        scale_c_kernel<<<grid, 256, 0, st>>>(C, M, N, out_dtype, out_layout, row_scale, tok_scale);
-        return (int)cudaGetLastError();
+        return launch_sgemm((const float *)W, (const float *)workspace, C, M, N, K, out_dtype, out_layout, st, row_scale,
+                            tok_scale);
     }
     return launch_gemm_bf16_tcgen05(workspace, W, C, M, N, K, out_dtype, out_layout, st, row_scale, tok_scale);
 }
@@ -367,7 +358,7 @@ extern "C" int b200ht_fused_gemm_static(const void *X, const void *W, void *C, i
 {
     using namespace b200ht;
     if (in_dtype != B200HT_F32 && in_dtype != B200HT_BF16) return B200HT_ERR_DTYPE;
-    if (M < 0 || N < 0 || K < 2) return B200HT_ERR_SIZE;
+    if (M < 0 || N < 0 || K < 2 || K > (1 << kMaxLogN) || !is_pow2((uint64_t)K)) return B200HT_ERR_SIZE;
     // Reject before anything is enqueued: the transformed tokens must fit the built-in array.
     const size_t need = b200ht_fused_gemm_workspace_bytes(M, N, K, in_dtype);
     if (need > (size_t)B200HT_STATIC_SCRATCH_BYTES) return B200HT_ERR_STATIC_SCRATCH;

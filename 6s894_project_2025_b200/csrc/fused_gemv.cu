@@ -266,12 +266,6 @@ __device__ __forceinline__ uint32_t lds32(uint32_t saddr)
     asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(v) : "r"(saddr));
     return v;
 }
-#ifdef B200HT_GEMV_TRACE
-__device__ unsigned long long g_gemv_trace[16];
-#define GV_TRACE(i) do { if (blockIdx.x == 50 && tid == 0) g_gemv_trace[i] = global_ns(); } while (0)
-#else
-#define GV_TRACE(i) do { } while (0)
-#endif
 
 template <int NT>
 __global__ void __launch_bounds__(GV_THREADS, 1)
@@ -296,7 +290,6 @@ gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bflo
     auto full_bar = [&](int s) { return bar_s + 8u * s; };
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    GV_TRACE(0);
 
     // rows of W owned by this CTA, in groups of group_rows; one ring item = (group, 64*kc-wide k chunk)
     const int row_begin = blockIdx.x * rows_per_cta;
@@ -342,7 +335,6 @@ gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bflo
         __syncthreads();
         if (warp == 0 && lane < (total_items < nstages ? total_items : nstages)) issue(lane);   // nstages <= 16
     };
-    GV_TRACE(1);
 
     // ------------------------------ X^T into shared memory ------------------------------
     // Every path issues all loads of a batch before the first store: a round trip to memory is long while the
@@ -468,7 +460,6 @@ gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bflo
         }
     }
     __syncthreads();
-    GV_TRACE(2);
     {
         // pass A covers 8 + ra bits, pass B the remaining jb (N <= 8192: jb <= 3)
         const int ra = logn - 8 < 2 ? logn - 8 : 2;
@@ -484,7 +475,6 @@ gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bflo
         else if (jb == 3) hxt_pass_b<3>(hxT, Bg, pitch, logn, scale / fa, tid);
         if (jb) __syncthreads();
     }
-    GV_TRACE(3);
 
     // ------------------------------ consume the ring ------------------------------
     const int g = lane >> 2, t = lane & 3;
@@ -521,7 +511,6 @@ gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bflo
             const int s = item % nstages;
             const uint32_t ph = (uint32_t)(item / nstages) & 1u;
             if (!mbar_wait(full_bar(s), ph, abort_flag, status)) return;
-            if (item == 0) GV_TRACE(4);
             const uint32_t stage = ring_s + (uint32_t)(s * stage_bytes);
             // this warp's k steps of the item, UNR at a time: all fragment loads first, then the products
             for (int ks0 = wj; ks0 < ksteps; ks0 += GV_GW * UNR) {
@@ -611,15 +600,8 @@ gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bflo
         }
         __syncthreads();
     }
-    GV_TRACE(6);
 }
 
-#ifdef B200HT_GEMV_TRACE
-extern "C" int b200ht_debug_gemv_trace(unsigned long long *out)
-{
-    return (int)cudaMemcpyFromSymbol(out, g_gemv_trace, sizeof(g_gemv_trace));
-}
-#endif
 
 // ---------------------------------------------------------------------------
 // fp32 (exact): H(X) in shared memory as fp32, one warp per row of W
@@ -692,20 +674,12 @@ gemv_f32_kernel(const float *W, const float *X, void *Y, int M, int N, int logn,
     }
 }
 
-static int sm_count()
-{
-    int dev = 0, n = 148;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    return n;
-}
-
 template <int NT>
 static int launch_bf16_nt(const void *W, const void *X, void *Y, int M, int N, int logn, int B, int b0,
                           int Bg, int gc, int out_dtype, float scale, size_t smem, cudaStream_t st)
 {
-    cudaError_t e =
-        cudaFuncSetAttribute(gemv_bf16_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
+    const int rc = ensure_dyn_smem((const void *)gemv_bf16_kernel<NT>, (int)smem);
+    if (rc) return rc;
     const int tiles = (M + 15) / 16;
     const int grid = tiles < sm_count() ? tiles : sm_count();
     note_launch();
@@ -773,9 +747,8 @@ static int launch_stream_nt(const void *W, const void *X, void *Y, int M, int N,
     CUtensorMap tw;
     int rc = encode_tmap_bf16_rows_chunks(&tw, W, (uint64_t)M, (uint64_t)N, (uint32_t)group_rows, (uint32_t)kc);
     if (rc) return rc;
-    cudaError_t e =
-        cudaFuncSetAttribute(gemv_bf16_stream_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
+    rc = ensure_dyn_smem((const void *)gemv_bf16_stream_kernel<NT>, (int)smem);
+    if (rc) return rc;
     return launch_pdl(gemv_bf16_stream_kernel<NT>, dim3(grid), dim3(GV_THREADS), smem, st, tw,
                       (const __nv_bfloat16 *)X, Y, M, N, logn, B, b0, Bg, out_dtype, scale, rows_per_cta, group_rows, kc,
                       stage_bytes, stages, red_in_ring ? 1 : 0, status_word_ptr());
@@ -816,9 +789,8 @@ int launch_gemv(const void *W, const void *X, void *Y, int M, int N, int B, int 
         for (int b0 = 0; b0 < B; b0 += bg_max) {
             const int Bg = (B - b0) < bg_max ? (B - b0) : bg_max;
             const size_t smem = (size_t)Bg * N * 4;
-            cudaError_t e = cudaFuncSetAttribute(gemv_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 (int)smem);
-            if (e != cudaSuccess) return (int)e;
+            const int rc = ensure_dyn_smem((const void *)gemv_f32_kernel, (int)smem);
+            if (rc) return rc;
             int grid = (M + 7) / 8;
             int per_sm = (int)((220 * 1024) / (smem + 1024));
             per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
@@ -827,7 +799,7 @@ int launch_gemv(const void *W, const void *X, void *Y, int M, int N, int B, int 
             note_launch();
             gemv_f32_kernel<<<grid, 256, smem, st>>>((const float *)W, (const float *)X, Y, M, N, logn, B, b0,
                                                      Bg, out_dtype, scale);
-            e = cudaGetLastError();
+            const cudaError_t e = cudaGetLastError();
             if (e != cudaSuccess) return (int)e;
         }
         return 0;

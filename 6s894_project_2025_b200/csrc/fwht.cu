@@ -121,9 +121,6 @@ __global__ void __launch_bounds__(256) fwht_reg_kernel(const uint4 *in, uint4 *o
 //           butterflies.  With 4 warps a warp owns 8 consecutive vectors of every chunk.
 //   pass 3: copy-out, 128 contiguous bytes per chunk and warp, by the warp that wrote them (no CTA barrier); with 8
 //           warps a CTA barrier and whole chunks
-// Measured (16384 rows, TB/s): 6.46 / 6.70 / 6.32 at n = 4096 / 8192 / 16384.  Earlier variants: four loads in flight
-// 5.4 / 6.2 / 6.0; a second pass without tensor cores (fp32 butterflies and shuffles) 6.0 at n = 4096 and slower
-// beyond; whole rows in registers at n = 4096 4.7.
 // ---------------------------------------------------------------------------
 template <int LOGN>
 struct SmemCfg {
@@ -132,7 +129,7 @@ struct SmemCfg {
     static constexpr int CPR = 1 << Q;
     static constexpr int NCHUNK = SLAB_ROWS * CPR;
     static constexpr int SMEM_BYTES = NCHUNK * 33 * 16;
-    static constexpr int NW = LOGN <= 14 ? 4 : 8;   // warps per CTA (measured: 4 with the warp-local copy-out is 2 % faster at n = 8192 and 16384)
+    static constexpr int NW = LOGN <= 14 ? 4 : 8;   // warps per CTA
 };
 
 template <int DT, int LOGN, bool SG>
@@ -364,8 +361,8 @@ static int launch_smem(const void *in, void *out, uint64_t rows, float scale, co
     const uint64_t blocks = (rows + Cfg::SLAB_ROWS - 1) / Cfg::SLAB_ROWS;
     if (blocks > 0x7fffffffull) return B200HT_ERR_SIZE;
     auto go = [&](auto kernel) -> int {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
-        if (e != cudaSuccess) return (int)e;
+        const int rc = ensure_dyn_smem((const void *)kernel, Cfg::SMEM_BYTES);
+        if (rc) return rc;
         return launch_pdl(kernel, dim3((unsigned)blocks), dim3(Cfg::NW * 32), (size_t)Cfg::SMEM_BYTES, st,
                           (const uint4 *)in, (uint4 *)out, rows, scale * 64.0f, (const uint4 *)signs);
     };
@@ -412,8 +409,8 @@ int launch_fwht_f32(const float *in, float *out, uint64_t rows, int logn, float 
     const uint64_t blocks = (rows + slab_rows - 1) / slab_rows;
     if (blocks > 0x7fffffffull) return B200HT_ERR_SIZE;
     const int smem = slab * 4;
-    cudaError_t e = cudaFuncSetAttribute(fwht_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return (int)e;
+    const int rc = ensure_dyn_smem((const void *)fwht_f32_kernel, smem);
+    if (rc) return rc;
     note_launch();
     fwht_f32_kernel<<<(unsigned)blocks, 256, smem, st>>>(in, out, rows, logn, slab_rows, scale, split);
     return (int)cudaGetLastError();

@@ -129,16 +129,6 @@ struct FtBars {
     __device__ uint32_t tmem_empty(int t) const { return base + 8u * (4 * FT_NBUF + 2 * FT_NSLOT + t); }
 };
 
-#ifdef B200HT_FWHT_TRACE
-__device__ unsigned long long g_ft_trace[16];
-#define FT_T(k) do { if (blockIdx.x == 7 && tid == 0) { const unsigned long long now_ = global_ns(); g_ft_trace[k] += now_ - tprev_; tprev_ = now_; } } while (0)
-#define FT_EV(slot, b) do { if (blockIdx.x == 7) ev_ts[(slot) * FT_NBUF + (b)] = global_ns(); } while (0)
-#define FT_ACC(k, from, to, b) do { if (blockIdx.x == 7) g_ft_trace[k] += ev_ts[(to) * FT_NBUF + (b)] - ev_ts[(from) * FT_NBUF + (b)]; } while (0)
-#else
-#define FT_T(k) do { } while (0)
-#define FT_EV(slot, b) do { } while (0)
-#define FT_ACC(k, from, to, b) do { } while (0)
-#endif
 
 template <int DT>
 __global__ void __launch_bounds__(FT_THREADS, 1)
@@ -154,9 +144,6 @@ fwht_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
     uint32_t *tmem_slot = (uint32_t *)(bar_mem + 8 * (4 * FT_NBUF + 3 * FT_NSLOT));
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
-#ifdef B200HT_FWHT_TRACE
-    __shared__ unsigned long long ev_ts[4 * FT_NBUF];   // [issue, full, staged, empty][buffer]
-#endif
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int cpr_log = logn - 7;                       // chunks per row, log2 (1..8)
     const bool pair_mode = cpr_log == 8;                // n = 32768: a row spans both tiles of a pair
@@ -246,8 +233,6 @@ fwht_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
                 const uint32_t ph = (uint32_t)(i / FT_NBUF) & 1u;
                 if (!mbar_wait(bars.empty(b), ph ^ 1u, abort_flag, status)) break;
                 const int tile = tile_of(i);
-                FT_EV(0, b);
-                if (i >= FT_NBUF) FT_ACC(9, 3, 0, b);   // idle: empty -> next issue
                 mbar_expect_tx(bars.full(b), FT_TILE_BYTES);
                 const uint32_t dst = buf_s + (uint32_t)(b * FT_TILE_BYTES);
                 tma_load_2d(dst, &tmIn, 0, tile * 128, bars.full(b));
@@ -272,8 +257,6 @@ fwht_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
             for (int i = 0; i < iters; ++i) {
                 const int b = i % FT_NBUF, t = i % FT_NSLOT;
                 if (!mbar_wait(bars.full(b), (uint32_t)(i / FT_NBUF) & 1u, abort_flag, status)) break;
-                FT_EV(1, b);
-                FT_ACC(6, 0, 1, b);   // load latency: issue -> full seen by the MMA warp
                 if (!mbar_wait(bars.tmem_empty(t), ((uint32_t)(i / FT_NSLOT) & 1u) ^ 1u, abort_flag, status)) break;
                 tc_fence_after();
                 const uint32_t a_s = buf_s + (uint32_t)(b * FT_TILE_BYTES);
@@ -313,9 +296,6 @@ fwht_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
         const int row = q * 32 + lane;        // chunk index inside the tile = TMEM lane
         const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
         bool ok = true;
-#ifdef B200HT_FWHT_TRACE
-        unsigned long long tprev_ = global_ns();
-#endif
         for (int i = grp; i < iters && ok; i += 2) {
             const int b = i % FT_NBUF, t = i % FT_NSLOT;
             const int io = i ^ 1, to = io % FT_NSLOT;          // the other tile of the pair and its slot
@@ -325,7 +305,6 @@ fwht_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
                 // D1 -> 16-bit -> MN-major B operand in the tile's own buffer (the first MMA is done with it)
                 if (!mbar_wait(bars.d1_full(t), tph, abort_flag, status)) { ok = false; break; }
                 tc_fence_after();
-                FT_T(0);
                 {
                     uint32_t r[4][32];
 #pragma unroll
@@ -348,14 +327,12 @@ fwht_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bars.b2_ready(b));
-                FT_T(1);
                 if (!mbar_wait(bars.d2_full(t), tph, abort_flag, status)) { ok = false; break; }
                 if (pair_mode && !mbar_wait(bars.d2_full(to), tpho, abort_flag, status)) { ok = false; break; }
             } else {
                 if (!mbar_wait(bars.d1_full(t), tph, abort_flag, status)) { ok = false; break; }
             }
             tc_fence_after();
-            FT_T(2);
             // final accumulator -> scale -> 16 bit -> output staging in the same buffer (the second MMA is done with it)
             const uint32_t dcol = (uint32_t)(t * 128);
             const uint32_t ocol = (uint32_t)(to * 128);
@@ -396,7 +373,6 @@ fwht_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
                         *(uint4 *)(bufp + sw128_off(row, c0 + 32 * h + 8 * v)) = o;
                     }
             }
-            FT_T(3);
             // accumulators drained and tile staged: hand the TMEM slot(s) to the MMA warp, the buffer to the store warp
             fence_proxy_async();
             tc_fence_before();
@@ -406,7 +382,6 @@ fwht_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
                 if (pair_mode) mbar_arrive(bars.tmem_empty(to));
                 mbar_arrive(bars.staged(b));
             }
-            FT_T(4);
         }
     }
     if (warp == 11 && lane == 0) {
@@ -415,8 +390,6 @@ fwht_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
         for (int i = 0; i < iters; ++i) {
             const int b = i % FT_NBUF;
             if (!mbar_wait(bars.staged(b), (uint32_t)(i / FT_NBUF) & 1u, abort_flag, status)) break;
-            FT_EV(2, b);
-            FT_ACC(7, 1, 2, b);   // compute residency: full -> staged
             const int tile = tile_of(i);
             const uint32_t src = buf_s + (uint32_t)(b * FT_TILE_BYTES);
             tma_store_2d(&tmOut, src, 0, tile * 128);
@@ -424,8 +397,6 @@ fwht_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
             bulk_commit();
             if (prev_b >= 0) {
                 bulk_wait_read1();                 // the previous store has read its buffer
-                FT_EV(3, prev_b);
-                FT_ACC(8, 2, 3, prev_b);   // store residency: staged -> empty
                 mbar_arrive(bars.empty(prev_b));
             }
             prev_b = b;
@@ -443,21 +414,6 @@ fwht_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
     }
 }
 
-#ifdef B200HT_FWHT_TRACE
-extern "C" int b200ht_debug_fwht_trace(unsigned long long *out, int clear)
-{
-    cudaError_t e = cudaMemcpyFromSymbol(out, g_ft_trace, sizeof(g_ft_trace));
-    if (clear) { unsigned long long z[16] = {0}; cudaMemcpyToSymbol(g_ft_trace, z, sizeof(z)); }
-    return (int)e;
-}
-#endif
-
-static int sm_count_ft()
-{
-    int dev = 0, n = 148;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    return n;
-}
 
 template <int DT>
 static int launch_ft(const void *in, void *out, uint64_t chunk_rows, int logn, float scale, cudaStream_t st)
@@ -467,11 +423,11 @@ static int launch_ft(const void *in, void *out, uint64_t chunk_rows, int logn, f
     if (rc) return rc;
     rc = encode_tmap_b16_2d(&tout, out, chunk_rows, 128, 128, DT);
     if (rc) return rc;
-    cudaError_t e = cudaFuncSetAttribute(fwht_tc_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, FT_SMEM_BYTES);
-    if (e != cudaSuccess) return (int)e;
+    rc = ensure_dyn_smem((const void *)fwht_tc_kernel<DT>, FT_SMEM_BYTES);
+    if (rc) return rc;
     const int ntiles = (int)((chunk_rows + 127) / 128);
     const int npairs = (ntiles + 1) / 2;
-    const int grid = npairs < sm_count_ft() ? npairs : sm_count_ft();
+    const int grid = npairs < sm_count() ? npairs : sm_count();
     // factors baked into the constants: 2^-3 for H_128, 2^-floor(hbits/2) for the second contraction
     const int cpr_log = logn - 7;
     const int hbits = cpr_log > 7 ? 7 : cpr_log;

@@ -309,10 +309,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             } else if (LAYOUT == B200HT_OUT_NM && OUT_DT == B200HT_BF16 && m0 + Cfg::BM <= M && n0 + TC_BN <= N &&
                        (ldc & 7) == 0 && ((uintptr_t)C & 15u) == 0) {
                 // Token-major bf16 result, tile fully inside C.  A lane owns a row m, so stores straight from the
-                // registers are 2 bytes per lane and 64 contiguous bytes per instruction (measured: 9-11 us per
-                // 256 x 256 tile).  Instead the four warps of a 128-row half stage 32 tokens x 128 rows in shared
-                // memory (two buffers, one named barrier per chunk) and write them out as 16 bytes per lane, 256
-                // contiguous bytes per token (3.3-4.2 us per tile).
+                // registers are 2 bytes per lane and 64 contiguous bytes per instruction.  Instead the four warps of
+                // a 128-row half stage 32 tokens x 128 rows in shared memory (two buffers, one named barrier per
+                // chunk) and write them out as 16 bytes per lane, 256 contiguous bytes per token.
                 unsigned char *stage_gen = gen_base + STAGES * STAGE_BYTES + h * 16384;
                 const int bar_id = 1 + h;
                 const int tok_sub = lane >> 4, seg = lane & 15;   // read-back: 2 tokens per instruction, 16 lanes each
@@ -423,20 +422,63 @@ static EncodeTiledFn get_encode_fn()
     return fn;
 }
 
+// Tensor maps depend only on (address, shape, box, element type), so the maps of buffers a caller reuses call after
+// call are kept in a small per-thread table (no lock); a miss encodes through the driver and replaces one entry.
+struct TmapKey {
+    const void *base;
+    uint64_t rows, cols, ld;
+    uint32_t box_rows, box_chunks;
+    int kind, dtype, dev;
+    bool operator==(const TmapKey &o) const
+    {
+        return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows &&
+               box_chunks == o.box_chunks && kind == o.kind && dtype == o.dtype && dev == o.dev;
+    }
+};
+struct TmapSlot {
+    TmapKey key;
+    CUtensorMap map;
+    bool valid;
+};
+constexpr int kTmapSlots = 64;
+
+template <typename Encode>
+static int tmap_cached(CUtensorMap *out, TmapKey key, Encode encode)
+{
+    static thread_local TmapSlot table[kTmapSlots];
+    if (cudaGetDevice(&key.dev) != cudaSuccess) key.dev = -1;
+    uint64_t h = (uint64_t)(uintptr_t)key.base * 0x9E3779B97F4A7C15ull;
+    h ^= (key.rows * 31 + key.cols * 17 + key.ld * 13 + key.box_rows * 7 + key.box_chunks * 5 + (uint64_t)key.kind * 3 +
+          (uint64_t)key.dtype) * 0xC2B2AE3D27D4EB4Full;
+    TmapSlot &slot = table[(h >> 32) % kTmapSlots];
+    if (slot.valid && slot.key == key) {
+        *out = slot.map;
+        return 0;
+    }
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return (int)cudaErrorNotSupported;
+    const CUresult r = encode(fn, out);
+    if (r != CUDA_SUCCESS) return (int)cudaErrorInvalidValue;
+    slot.key = key;
+    slot.map = *out;
+    slot.valid = true;
+    return 0;
+}
+
 int encode_tmap_b16_2d(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows,
                        int dtype)
 {
-    EncodeTiledFn fn = get_encode_fn();
-    if (!fn) return (int)cudaErrorNotSupported;
-    const cuuint64_t dims[2] = {cols, rows};
-    const cuuint64_t strides[1] = {cols * 2};
-    const cuuint32_t box[2] = {64, box_rows};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUtensorMapDataType dt =
-        dtype == B200HT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    CUresult r = fn(map, dt, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+    return tmap_cached(map, TmapKey{base, rows, cols, cols, box_rows, 0, 0, dtype, 0},
+                       [&](EncodeTiledFn fn, CUtensorMap *m) {
+        const cuuint64_t dims[2] = {cols, rows};
+        const cuuint64_t strides[1] = {cols * 2};
+        const cuuint32_t box[2] = {64, box_rows};
+        const cuuint32_t estr[2] = {1, 1};
+        const CUtensorMapDataType dt =
+            dtype == B200HT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+        return fn(m, dt, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    });
 }
 
 int encode_tmap_bf16_2d(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows)
@@ -450,39 +492,31 @@ int encode_tmap_bf16_2d(CUtensorMap *map, const void *base, uint64_t rows, uint6
 int encode_tmap_bf16_rows_chunks(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols,
                                  uint32_t box_rows, uint32_t box_chunks)
 {
-    EncodeTiledFn fn = get_encode_fn();
-    if (!fn) return (int)cudaErrorNotSupported;
-    const cuuint64_t dims[3] = {64, rows, cols / 64};
-    const cuuint64_t strides[2] = {cols * 2, 128};
-    const cuuint32_t box[3] = {64, box_rows, box_chunks};
-    const cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+    return tmap_cached(map, TmapKey{base, rows, cols, cols, box_rows, box_chunks, 1, B200HT_BF16, 0},
+                       [&](EncodeTiledFn fn, CUtensorMap *m) {
+        const cuuint64_t dims[3] = {64, rows, cols / 64};
+        const cuuint64_t strides[2] = {cols * 2, 128};
+        const cuuint32_t box[3] = {64, box_rows, box_chunks};
+        const cuuint32_t estr[3] = {1, 1, 1};
+        return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    });
 }
 
 // Output map for the TMA-store epilogue: rows x cols of fp32 or bf16, box = 32 rows x 128 bytes, 128-byte swizzle.
 static int encode_tmap_out_2d(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint64_t ld, int dtype)
 {
-    EncodeTiledFn fn = get_encode_fn();
-    if (!fn) return (int)cudaErrorNotSupported;
-    const uint64_t esz = dtype == B200HT_F32 ? 4 : 2;
-    const cuuint64_t dims[2] = {cols, rows};
-    const cuuint64_t strides[1] = {ld * esz};
-    const cuuint32_t box[2] = {(cuuint32_t)(128 / esz), 32};
-    const cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, dtype == B200HT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
-                    const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
-}
-
-static int sm_count_tc()
-{
-    int dev = 0, n = 148;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    return n;
+    return tmap_cached(map, TmapKey{base, rows, cols, ld, 32, 0, 2, dtype, 0}, [&](EncodeTiledFn fn, CUtensorMap *m) {
+        const uint64_t esz = dtype == B200HT_F32 ? 4 : 2;
+        const cuuint64_t dims[2] = {cols, rows};
+        const cuuint64_t strides[1] = {ld * esz};
+        const cuuint32_t box[2] = {(cuuint32_t)(128 / esz), 32};
+        const cuuint32_t estr[2] = {1, 1};
+        return fn(m, dtype == B200HT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                  const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    });
 }
 
 template <int OUT_DT, int LAYOUT, int MT>
@@ -504,11 +538,10 @@ static int launch_tc_mt(const void *Y, const void *W, void *C, int M, int N, int
             encode_tmap_out_2d(&tc, C, (uint64_t)M, (uint64_t)N, (uint64_t)ldc, OUT_DT) == 0)
             tma_store = 1;
     }
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<OUT_DT, LAYOUT, MT>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
-    if (e != cudaSuccess) return (int)e;
+    rc = ensure_dyn_smem((const void *)gemm_tc_kernel<OUT_DT, LAYOUT, MT>, Cfg::SMEM_BYTES);
+    if (rc) return rc;
     const int tiles = ((M + Cfg::BM - 1) / Cfg::BM) * ((N + TC_BN - 1) / TC_BN) - skip_last_tiles;
-    const int grid = tiles < sm_count_tc() ? tiles : sm_count_tc();
+    const int grid = tiles < sm_count() ? tiles : sm_count();
     return launch_pdl(gemm_tc_kernel<OUT_DT, LAYOUT, MT>, dim3(grid), dim3(Cfg::THREADS), (size_t)Cfg::SMEM_BYTES, st,
                       tw, ty, tc, tma_store, C, M, N, K, ldc, tiles, pdl_mode, row_scale, tok_scale, status_word_ptr());
 }
@@ -529,7 +562,7 @@ static int launch_tc(const void *Y, const void *W, void *C, int M, int N, int K,
         return !(e && e[0] == '0');
     }();
     const size_t ldc = LAYOUT == B200HT_OUT_MN ? (size_t)N : (size_t)M;
-    const long sms = sm_count_tc();
+    const long sms = sm_count();
     const long nt = (N + TC_BN - 1) / TC_BN;
     const long mt256 = (M + 255) / 256;
     const long tiles128 = (long)((M + 127) / 128) * nt, tiles256 = mt256 * nt;

@@ -47,13 +47,18 @@ def test_missing_rank_is_detected_by_the_survivor(tmp_path):
         try:
             pkg.gather_result(local, 6, "nm")             # step 2: the peer is gone
         except Exception as e:                            # noqa: BLE001
-            print("survivor saw:", type(e).__name__)
+            print("survivor saw:", type(e).__name__, flush=True)
+            open({str(tmp_path / "survivor.txt")!r}, "w").write(type(e).__name__)
             sys.exit(0)
-        sys.exit(3)
+        sys.exit(3)                                       # the collective returned although the peer never joined
     """))
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="1")
     r = subprocess.run(
         [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
          "--master-addr", "127.0.0.1", "--master-port", "29633", str(script)],
         capture_output=True, text=True, env=env, timeout=300)
+    # both workers must exit 0: rank 1 by leaving, rank 0 by catching the error of its collective (exit code 3 would
+    # mean the collective returned, any other code that the worker crashed)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert (tmp_path / "survivor.txt").exists(), r.stdout + r.stderr
     assert "survivor saw:" in r.stdout + r.stderr, r.stdout + r.stderr

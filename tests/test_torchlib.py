@@ -84,3 +84,50 @@ def test_cuda_graph_with_the_two_launch_gemm(pkg):
     torch.cuda.synchronize()
     assert torch.equal(got, expect) and torch.equal(got2, expect2)
     assert pkg.device_status() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("backend", ["aot_eager", "inductor"])
+def test_torch_compile_fullgraph_matches_eager(pkg, backend):
+    """A module whose forward calls the three registered operators compiles with fullgraph=True (no graph break at
+    the custom ops: the fake-tensor functions give the compiler their shapes) and returns what eager returns, bit
+    for bit; the backward of the compiled transform is the transform of the incoming gradient."""
+
+    class Block(torch.nn.Module):
+        def __init__(self, W, Wv):
+            super().__init__()
+            self.W = torch.nn.Parameter(W, requires_grad=False)
+            self.Wv = torch.nn.Parameter(Wv, requires_grad=False)
+
+        def forward(self, x, X, Xv):
+            y = torch.ops.b200ht.hadamard_transform(x, x.shape[-1] ** -0.5)
+            c = torch.ops.b200ht.fused_ht_gemm(X, self.W, X.shape[-1] ** -0.5, True, True)
+            v = torch.ops.b200ht.fused_ht_gemv(self.Wv, Xv, Xv.shape[0] ** -0.5, False)
+            return y * 2, c, v + 1
+
+    g = torch.Generator(device="cuda").manual_seed(7)
+    x = torch.randn(32, 1024, generator=g, device="cuda").bfloat16()
+    X = torch.randn(300, 512, generator=g, device="cuda").bfloat16()
+    W = torch.randn(192, 512, generator=g, device="cuda").bfloat16()
+    Wv = (torch.randn(256, 2048, generator=g, device="cuda") / 45).bfloat16()
+    Xv = torch.randn(2048, 4, generator=g, device="cuda").bfloat16()
+    mod = Block(W, Wv)
+    eager = mod(x, X, Xv)
+    torch._dynamo.reset()
+    compiled = torch.compile(mod, fullgraph=True, backend=backend)
+    got = compiled(x, X, Xv)
+    for a, b in zip(got, eager):
+        assert a.shape == b.shape and a.dtype == b.dtype
+        assert torch.equal(a, b)
+
+    # backward through the compiled transform
+    def f(t):
+        return torch.ops.b200ht.hadamard_transform(t, 1.0 / 16).float().square().sum()
+
+    t0 = torch.randn(8, 256, generator=g, device="cuda").bfloat16()
+    te = t0.clone().requires_grad_(True)
+    f(te).backward()
+    tc = t0.clone().requires_grad_(True)
+    torch.compile(f, fullgraph=True, backend=backend)(tc).backward()
+    assert torch.allclose(tc.grad.float(), te.grad.float(), atol=2e-2, rtol=2e-2)
+    assert pkg.device_status() == 0

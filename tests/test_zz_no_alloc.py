@@ -68,3 +68,70 @@ def test_static_scratch_entry_rejects_oversized_problems(lib):
     assert "static scratch" in lib.error_string(rc)
     rc = l.b200ht_fused_gemm_static(p, p, p, 128, n_fit // 2 + 1, K, lib.F32, lib.F32, lib.OUT_MN, 1.0, None)
     assert rc == -9
+
+
+def test_static_entry_back_to_back_through_the_two_launch_contraction(lib):
+    """M=4096, N=2560, K=64 needs 16 x 10 = 160 tiles of 256 rows on 148 SMs, so the contraction is two launches
+    (whole waves of 256-row tiles, then a 128-row tail) tied together by programmatic dependencies.  Two such calls
+    are enqueued back to back on one stream with no synchronisation in between: the second call's transform
+    overwrites the built-in array while the first call's tail may still be draining, unless the ordering inside the
+    library holds.  Both results must equal the workspace entry's, bit for bit (same kernels, same inputs)."""
+    l = lib.load()
+    g = torch.Generator().manual_seed(12)
+    M, N, K = 4096, 2560, 64
+    Xa = torch.randn(N, K, generator=g).bfloat16().cuda()
+    Xb = torch.randn(N, K, generator=g).bfloat16().cuda()
+    W = torch.randn(M, K, generator=g).bfloat16().cuda()
+    st = torch.cuda.current_stream().cuda_stream
+    sc = float(K ** -0.5)
+    ca = torch.empty(N, M, dtype=torch.bfloat16, device="cuda")
+    cb = torch.empty(N, M, dtype=torch.bfloat16, device="cuda")
+    for X, C in ((Xa, ca), (Xb, cb)):      # no sync between the two calls
+        rc = l.b200ht_fused_gemm_static(X.data_ptr(), W.data_ptr(), C.data_ptr(), M, N, K, lib.BF16, lib.BF16,
+                                        lib.OUT_NM, sc, st)
+        assert rc == 0, lib.error_string(rc)
+    torch.cuda.synchronize()
+    ws = torch.empty(l.b200ht_fused_gemm_workspace_bytes(M, N, K, lib.BF16), dtype=torch.uint8, device="cuda")
+    for X, C in ((Xa, ca), (Xb, cb)):
+        ref = torch.empty_like(C)
+        rc = l.b200ht_fused_gemm(X.data_ptr(), W.data_ptr(), ref.data_ptr(), M, N, K, lib.BF16, lib.BF16, lib.OUT_NM,
+                                 sc, ws.data_ptr(), ws.numel(), st)
+        assert rc == 0, lib.error_string(rc)
+        torch.cuda.synchronize()
+        assert torch.equal(C, ref)
+    assert l.b200ht_device_status(1) == 0
+
+
+def test_static_entry_leaves_free_device_memory_unchanged(lib):
+    """The point of the entry: after one warm-up call of a given shape class (which may make the driver load the
+    kernels it needs), further calls change the device's free memory by nothing."""
+    l = lib.load()
+    g = torch.Generator().manual_seed(13)
+    M, N, K = 512, 640, 1024
+    X = torch.randn(N, K, generator=g).bfloat16().cuda()
+    W = torch.randn(M, K, generator=g).bfloat16().cuda()
+    C = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+
+    def call():
+        rc = l.b200ht_fused_gemm_static(X.data_ptr(), W.data_ptr(), C.data_ptr(), M, N, K, lib.BF16, lib.F32,
+                                        lib.OUT_MN, float(K ** -0.5), st)
+        assert rc == 0, lib.error_string(rc)
+
+    call()
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        call()
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0
+
+
+def test_static_entry_checks_the_transform_size_before_the_scratch_size(lib):
+    l = lib.load()
+    x = torch.zeros(16, dtype=torch.uint8, device="cuda")
+    p = x.data_ptr()
+    # K not a power of two, and so large that N*K would also exceed the array: the size error wins
+    rc = l.b200ht_fused_gemm_static(p, p, p, 128, 1 << 20, 3000, lib.BF16, lib.F32, lib.OUT_MN, 1.0, None)
+    assert rc == -2
