@@ -18,7 +18,12 @@ no collective on the data path), so total work is fixed: strong scaling.
             fused call (transform kernel + GEMM kernel, so a lower bound for the
             GEMM kernel alone) against the measured sustained bf16 peak
   fwht      secondary block: standalone transform of (16384, n) bf16, n = 2^8..
-            2^15, HBM GB/s against the measured copy bandwidth
+            2^15, in place on >= 512 MB of rotating buffers, HBM GB/s against the
+            measured copy bandwidth; roofline_fwht is the WORST n >= 512
+  fwht_2p30_elements  the reference's benchmark shape: 2^30 elements per n, in place
+  sustained the fused call looped for >= 2 s on every rank with the SM clock
+            sampled: TFLOP/s, median MHz, TFLOP/s per MHz (scaling at equal clocks)
+  host_call_cost  host microseconds per C-ABI call (enqueue only)
   gemv      secondary block: fused GEMV, W 4096 x 4096 bf16, B = 1, 4, 16, GB/s
   c3        secondary block: fused W.H(X) at K=1024, 4096 tokens, M=4096, fp32 and bf16
   k4096     secondary block: fused W.H(X) at K=4096, M=16384, 16384 tokens, bf16, TFLOP/s
@@ -69,14 +74,15 @@ class ClockSampler:
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index: int):
+    def __init__(self, gpu_index: int, period_ms: int = 20):
         self.gpu_index = gpu_index
+        self.period_ms = period_ms
         self.proc = None
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "20",
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", str(self.period_ms),
                  "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -165,26 +171,33 @@ def run_reference_arm(args):
 # ----------------------------------------------------------------------------
 # GPU arm
 # ----------------------------------------------------------------------------
+# DRAM read + write bytes per element of one transform launch (steady state of the rotating in-place loop below), from
+# a one-pass ncu capture of `bench.py --profile-case fwht-sweep` with the caches left alone between launches
+# (profiles/fwht_sweep_dram_bytes.md); the algorithmic figure is 4 bytes per element.
+FWHT_DRAM_BYTES_PER_ELEMENT = {}
+
+
 def time_fwht_sweep(pkg, torch, peaks, rows=16384, reps=10):
-    """Standalone transform, (rows, n) bf16, n = 2^8..2^15.  Buffers are rotated so
-    that every launch reads data that is not L2-resident (>= 512 MB per rotation)."""
+    """Standalone transform, (rows, n) bf16, n = 2^8..2^15, IN PLACE on rotating buffers (the reference's loop
+    transforms in place too: bench/bench.py:206-238 there).  Per n at least 512 MB of distinct buffers are read and
+    written between two uses of the same buffer, four times the 126 MB L2, so neither the reads nor the write-back
+    of a launch are served by the cache.  H with scale 1/sqrt(n) is an involution: values stay bounded."""
     out = {}
+    lib = pkg._lib.load()
+    st = torch.cuda.current_stream().cuda_stream
     for logn in range(8, 16):
         n = 1 << logn
         nbytes = rows * n * 2
         nbuf = max(2, math.ceil((512 << 20) / nbytes))
         bufs = [torch.randn(rows, n, device="cuda", dtype=torch.float32).bfloat16() for _ in range(nbuf)]
-        dst = torch.empty_like(bufs[0])
-        lib = pkg._lib.load()
-        st = torch.cuda.current_stream().cuda_stream
         sc = float(n ** -0.5)
 
         def call(b):
-            rc = lib.b200ht_fwht(b.data_ptr(), dst.data_ptr(), rows, n, pkg._lib.BF16, sc, st)
+            rc = lib.b200ht_fwht(b.data_ptr(), b.data_ptr(), rows, n, pkg._lib.BF16, sc, st)
             if rc:
                 raise RuntimeError(pkg._lib.error_string(rc))
 
-        for b in bufs[:3]:
+        for b in bufs:
             call(b)
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -196,8 +209,45 @@ def time_fwht_sweep(pkg, torch, peaks, rows=16384, reps=10):
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / (reps * nbuf)
         gbs = rows * n * 4 / (ms * 1e-3) / 1e9
+        bpe = FWHT_DRAM_BYTES_PER_ELEMENT.get(n)
+        out[str(n)] = {"ms": ms, "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
+                       "traffic": None if bpe is None else bpe * rows * n, "buffers": nbuf}
+        del bufs
+    return out
+
+
+def time_fwht_reference_shape(pkg, torch, peaks, reps=5):
+    """The reference's own benchmark shape for the transform: 2^30 elements per n (rows = 2^30 / n), bf16, in place on
+    one 2 GB buffer (bench/bench.py:138, 268-276 there); 4.3 GB of traffic per launch, far beyond L2."""
+    out = {}
+    lib = pkg._lib.load()
+    st = torch.cuda.current_stream().cuda_stream
+    total = 1 << 30
+    buf = torch.randn(total // 2, device="cuda", dtype=torch.float32).bfloat16()
+    buf = torch.cat([buf, buf.flip(0)])
+    for logn in range(8, 16):
+        n = 1 << logn
+        rows = total // n
+        sc = float(n ** -0.5)
+
+        def call():
+            rc = lib.b200ht_fwht(buf.data_ptr(), buf.data_ptr(), rows, n, pkg._lib.BF16, sc, st)
+            if rc:
+                raise RuntimeError(pkg._lib.error_string(rc))
+
+        for _ in range(2):
+            call()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(2 * reps):     # an even count: the buffer ends as it started
+            call()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / (2 * reps)
+        gbs = total * 4 / (ms * 1e-3) / 1e9
         out[str(n)] = {"ms": ms, "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"]}
-        del bufs, dst
+    del buf
     return out
 
 
@@ -348,6 +398,127 @@ def time_k4096(pkg, torch, peaks, reps=5):
             "frac_of_nominal_2250": tf / 2250.0}
 
 
+def time_sustained(torch, dist, step, flops_rank, rank, local_rank, world, seconds=2.0):
+    """The fused call back to back for at least `seconds` on every rank at once, with this rank's SM clock sampled
+    meanwhile: TFLOP/s, median SM MHz and TFLOP/s per MHz.  A burst of a few milliseconds runs at the boost clock,
+    a long loop at whatever the 1 kW power cap allows, so scaling across N is read here at equal clock state."""
+    for _ in range(2):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    step()
+    e1.record()
+    torch.cuda.synchronize()
+    calls = max(4, int(seconds * 1e3 / max(e0.elapsed_time(e1), 1e-3)) + 1)
+    if world > 1:
+        c = torch.tensor([calls], device="cuda")
+        dist.all_reduce(c, op=dist.ReduceOp.MAX)
+        calls = int(c.item())
+        dist.barrier()
+    sampler = ClockSampler(local_rank, period_ms=50)
+    sampler.start()
+    e0.record()
+    for _ in range(calls):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1)
+    mine = torch.tensor([ms, flops_rank * calls / (ms * 1e-3) / 1e12, float(clocks["sm_mhz"] or 0.0)], device="cuda")
+    if world > 1:
+        allr = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(allr, mine)
+    else:
+        allr = [mine]
+    per_rank = [[float(v) for v in t.tolist()] for t in allr]
+    t_max = max(r[0] for r in per_rank)
+    tf = flops_rank * calls * world / (t_max * 1e-3) / 1e12
+    mhz = [r[2] for r in per_rank]
+    med = statistics.median(mhz) if mhz else 0.0
+    return {"seconds": t_max * 1e-3, "calls": calls, "tflops": tf, "tflops_per_gpu": [r[1] for r in per_rank],
+            "sm_mhz_per_gpu": mhz, "sm_mhz_median": med, "tflops_per_gpu_per_mhz": (tf / world / med) if med else None,
+            "reasons": clocks["reasons"]}
+
+
+def time_copy_floor(torch, dist, pipe, Xh, Ch, world, steps=3):
+    """The host<->device copies of one end-to-end step alone: the same chunks on the same streams as HostPipeline,
+    one cudaMemcpyAsync per chunk and direction, no kernels, on all ranks at once.  An end-to-end step cannot be
+    faster than this; max over ranks, in ms."""
+    n = int(Xh.shape[0])
+
+    def copies():
+        cur = torch.cuda.current_stream()
+        for st in pipe.streams:
+            st.wait_stream(cur)
+        for i, t0 in enumerate(range(0, n, pipe.chunk)):
+            t1 = min(t0 + pipe.chunk, n)
+            k = i % len(pipe.streams)
+            with torch.cuda.stream(pipe.streams[k]):
+                pipe.x[k][: t1 - t0].copy_(Xh[t0:t1], non_blocking=True)
+                Ch[t0:t1].copy_(pipe.c[k][: t1 - t0], non_blocking=True)
+        for st in pipe.streams:
+            cur.wait_stream(st)
+
+    copies()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        copies()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / steps], device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def time_host_call_cost(pkg, torch, calls=200):
+    """Host time of one C-ABI call (CPU clock around a burst of calls that are only enqueued, no synchronisation in
+    between; the burst is shorter than the launch queue).  The trivial transform (one row of two elements) is the
+    floor of a launch through the library; the GEMV adds a tensor map and a shared-memory attribute, which come from
+    per-thread / per-device caches after the first call."""
+    lib = pkg._lib.load()
+    st = torch.cuda.current_stream().cuda_stream
+    g = torch.Generator(device="cuda").manual_seed(8)
+    tiny = torch.zeros(8, dtype=torch.bfloat16, device="cuda")
+    x = torch.randn(64, 1024, generator=g, device="cuda").bfloat16()
+    W = (torch.randn(256, 4096, generator=g, device="cuda") / 64).bfloat16()
+    X = torch.randn(4096, 4, generator=g, device="cuda").bfloat16()
+    Y = torch.empty(256, 4, dtype=torch.float32, device="cuda")
+    X3 = torch.randn(256, 1024, generator=g, device="cuda").bfloat16()
+    W3 = torch.randn(256, 1024, generator=g, device="cuda").bfloat16()
+    C3 = torch.empty(256, 256, dtype=torch.float32, device="cuda")
+    ws = torch.empty(pkg.fused_gemm_workspace_bytes(256, 256, 1024, torch.bfloat16), dtype=torch.uint8, device="cuda")
+    BF16, F32 = pkg._lib.BF16, pkg._lib.F32
+    cases = {
+        "fwht_trivial": lambda: lib.b200ht_fwht(tiny.data_ptr(), tiny.data_ptr(), 1, 2, BF16, 1.0, st),
+        "fwht_64x1024": lambda: lib.b200ht_fwht(x.data_ptr(), x.data_ptr(), 64, 1024, BF16, 1.0 / 32, st),
+        "gemv_256x4096_b4": lambda: lib.b200ht_fused_gemv(W.data_ptr(), X.data_ptr(), Y.data_ptr(), 256, 4096, 4, BF16,
+                                                          F32, 1.0 / 64, st),
+        "gemm_256x256x1024": lambda: lib.b200ht_fused_gemm(X3.data_ptr(), W3.data_ptr(), C3.data_ptr(), 256, 256, 1024,
+                                                           BF16, F32, pkg._lib.OUT_MN, 1.0 / 32, ws.data_ptr(),
+                                                           ws.numel(), st),
+    }
+    out = {}
+    for name, fn in cases.items():
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        best = 1e30
+        for _ in range(3):
+            t0 = time.perf_counter()
+            for _ in range(calls):
+                fn()
+            best = min(best, time.perf_counter() - t0)
+            torch.cuda.synchronize()
+        out[name] = {"host_us_per_call": best / calls * 1e6}
+    return out
+
+
 def run_gpu_arm(args):
     import torch
     import torch.distributed as dist
@@ -434,8 +605,13 @@ def run_gpu_arm(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t.item())
     e2e_val = flops_total / (e2e_ms * 1e-3) / 1e12
+    copy_floor_ms = time_copy_floor(torch, dist, pipe, Xh, Ch, world)
+    del pipe, Xh, Ch
 
+    sustained = time_sustained(torch, dist, step, 2.0 * M_DIM * n_local * K_DIM, rank, local_rank, world)
     fwht = time_fwht_sweep(pkg, torch, peaks)
+    fwht_ref_shape = time_fwht_reference_shape(pkg, torch, peaks)
+    host_cost = time_host_call_cost(pkg, torch) if rank == 0 else None
     gemv = time_gemv(pkg, torch, peaks)
     c3 = time_c3(pkg, torch, peaks)
     k4096 = time_k4096(pkg, torch, peaks)
@@ -464,14 +640,16 @@ def run_gpu_arm(args):
                              "then W matmul, fp32 torch on host cores"}
         achieved = 2.0 * M_DIM * n_local * K_DIM / (ms_local * 1e-3) / 1e12
         peak = peaks["bf16_tflops_sustained"]
-        best_fwht = max(fwht.values(), key=lambda v: v["gbs"])
+        # the transform's roofline line is its WORST size from n = 512 up (n = 256 moves 8 MB per launch and is
+        # bound by launch latency, which the per-n table shows)
+        worst_n, worst_fwht = min(((k, v) for k, v in fwht.items() if int(k) >= 512), key=lambda kv: kv[1]["gbs"])
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "c5 fused W.H(X): K=8192, M=28672, 16384 tokens split by token columns",
                        "tokens_per_gpu": n_local, "parallelism": f"token-shard x{world}, W replicated",
-                       "l2": "inputs (W 470 MB + tokens) exceed the 126 MB L2; fwht sweep rotates >= 512 MB of buffers",
+                       "l2": "inputs (W 470 MB + tokens) exceed the 126 MB L2; fwht sweep runs in place on >= 512 MB of rotating buffers",
                        "out": "bf16 token-major"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak,
@@ -481,17 +659,23 @@ def run_gpu_arm(args):
                          "traffic": 6.906e9 * n_local / N_TOKENS, "traffic_unit": "B/launch",
                          "peak_source": f"{peaks['source']} sustained cuBLAS bf16 (burst {peaks['bf16_tflops']})",
                          "frac_of_burst": achieved / peaks["bf16_tflops"]},
-            "roofline_fwht": {"bound": "hbm", "achieved": best_fwht["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                              "frac": best_fwht["gbs"] / peaks["hbm_gbs"], "traffic": None,
+            "roofline_fwht": {"bound": "hbm", "achieved": worst_fwht["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                              "frac": worst_fwht["gbs"] / peaks["hbm_gbs"], "traffic": worst_fwht["traffic"],
+                              "n": int(worst_n), "rule": "minimum over n >= 512 of the 16384-row sweep",
                               "peak_source": f"{peaks['source']} copy bandwidth"},
             "fwht": fwht,
+            "fwht_2p30_elements": fwht_ref_shape,
+            "sustained": sustained,
+            "host_call_cost": host_cost,
             "gemv": gemv,
             "c3": c3,
             "k4096": k4096,
             "gemv_rows": gemv_rows,
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": X.numel() * 2 * world, "d2h_bytes_per_step": C.numel() * 2 * world},
+                    "h2d_bytes_per_step": X.numel() * 2 * world, "d2h_bytes_per_step": C.numel() * 2 * world,
+                    # the same copies without any kernel (max over ranks): the PCIe / host-memory floor of a step
+                    "copy_floor_ms": copy_floor_ms, "frac_of_copy_floor": copy_floor_ms / e2e_ms},
             "gpu_launches": gpu_launches,
             "clocks": clocks,
         }
@@ -530,6 +714,25 @@ def run_profile_case(case: str):
             for b in bufs:
                 y = pkg.hadamard_transform(b)
             print("fwht case", n, float(y.float().abs().mean()))
+    elif case == "fwht-sweep":
+        # the bench's transform loop (16384 rows, n = 2^8..2^15, in place on >= 512 MB of rotating buffers), two
+        # rotations per n: a one-pass capture of the DRAM counters with `--cache-control none` sees the steady state
+        # of the second rotation, in which every launch's reads miss L2 and as many dirty lines are written back as
+        # the launch produces
+        lib = pkg._lib.load()
+        st = torch.cuda.current_stream().cuda_stream
+        rows = 16384
+        for logn in range(8, 16):
+            n = 1 << logn
+            nbuf = max(2, math.ceil((512 << 20) / (rows * n * 2)))
+            bufs = [torch.randn(rows, n, generator=g, device="cuda").bfloat16() for _ in range(nbuf)]
+            for _ in range(2):
+                for b in bufs:
+                    rc = lib.b200ht_fwht(b.data_ptr(), b.data_ptr(), rows, n, pkg._lib.BF16, float(n ** -0.5), st)
+                    assert rc == 0
+            torch.cuda.synchronize()
+            print("fwht-sweep case", n, nbuf, float(bufs[0].float().abs().mean()))
+            del bufs
     else:                   # fused GEMV, W 4096 x 4096 bf16, B = 16 and 1, distinct W buffers
         Ws = [(torch.randn(4096, 4096, generator=g, device="cuda") / 64).bfloat16() for _ in range(6)]
         for B in (16, 1):
@@ -540,17 +743,100 @@ def run_profile_case(case: str):
     torch.cuda.synchronize()
 
 
+def run_compare(which: str):
+    """Same-box library comparators (``--compare cublas``), one JSON line.  Nothing here is on the product path: the
+    library kernels are timed beside this repository's calls on the same buffers.
+      c5    the bench shape in alternating 10-call blocks: b200ht_fused_gemm | torch.matmul (cuBLAS) on already
+            transformed tokens | b200ht_fwht followed by that matmul
+      gemv  W 4096 x 4096 bf16 on 16 rotating copies, B = 1, 4, 16: b200ht_fused_gemv | F.linear (cuBLAS, no
+            transform) | torch.sum(W) | a copy of W
+    """
+    import torch
+    import torch.nn.functional as F
+
+    assert which == "cublas"
+    pkg = importlib.import_module("6s894_project_2025_b200")
+    torch.cuda.set_device(0)
+    g = torch.Generator(device="cuda").manual_seed(4)
+    ev = lambda: torch.cuda.Event(enable_timing=True)   # noqa: E731
+
+    def timed(fn, reps):
+        e0, e1 = ev(), ev()
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    W = (torch.randn(M_DIM, K_DIM, generator=g, device="cuda") / math.sqrt(K_DIM)).bfloat16()
+    X = torch.randn(N_TOKENS, K_DIM, generator=g, device="cuda").bfloat16()
+    Y = pkg.hadamard_transform(X)
+    C = torch.empty(N_TOKENS, M_DIM, dtype=torch.bfloat16, device="cuda")
+    ws = torch.empty(pkg.fused_gemm_workspace_bytes(M_DIM, N_TOKENS, K_DIM, torch.bfloat16), dtype=torch.uint8,
+                     device="cuda")
+    legs = {
+        "b200ht_fused_gemm": lambda: pkg.fused_ht_gemm(X, W, out=C, out_layout="nm", out_dtype=torch.bfloat16,
+                                                       workspace=ws),
+        "cublas_gemm_only": lambda: torch.matmul(Y, W.t(), out=C),
+        "b200ht_fwht_then_cublas": lambda: torch.matmul(pkg.hadamard_transform(X), W.t(), out=C),
+    }
+    for fn in legs.values():
+        for _ in range(3):
+            fn()
+    torch.cuda.synchronize()
+    c5 = {k: [] for k in legs}
+    for _ in range(4):
+        for k, fn in legs.items():
+            c5[k].append(timed(fn, 10))
+    del W, X, Y, C, ws
+
+    M = N = 4096
+    Ws = [(torch.randn(M, N, generator=g, device="cuda") / 64).bfloat16() for _ in range(16)]
+    dst = torch.empty_like(Ws[0])
+    gemv = {}
+    for B in (1, 4, 16):
+        Xc = torch.randn(N, B, generator=g, device="cuda").bfloat16()
+        Xr = Xc.t().contiguous()
+        out = torch.empty(M, B, dtype=torch.float32, device="cuda")
+        state = {"i": 0}
+
+        def nxt():
+            state["i"] = (state["i"] + 1) % len(Ws)
+            return Ws[state["i"]]
+
+        row = {
+            "b200ht_fused_gemv": lambda: pkg.fused_ht_gemv(nxt(), Xc, out=out),
+            "cublas_linear_no_transform": lambda: F.linear(Xr, nxt()),
+            "torch_sum_W": lambda: torch.sum(nxt()),
+            "copy_W": lambda: dst.copy_(nxt()),
+        }
+        res = {}
+        for k, fn in row.items():
+            for _ in range(5):
+                fn()
+            torch.cuda.synchronize()
+            res[k] = timed(fn, 160) * 1e3
+        gemv[str(B)] = res
+    print(json.dumps({"compare": "cublas", "c5_ms_per_call_blocks_of_10": c5, "gemv_us_per_call": gemv,
+                      "note": "device time by CUDA events; the GEMV rows include the Python call of each leg"}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--profile-case", default=None, choices=["gemm", "gemm-full", "fwht", "gemv", "c3"],
+    ap.add_argument("--profile-case", default=None, choices=["gemm", "gemm-full", "fwht", "fwht-sweep", "gemv", "c3"],
                     help="run a few launches of ONE kernel on a reduced shape and exit (for ncu captures)")
+    ap.add_argument("--compare", default=None, choices=["cublas"],
+                    help="time library comparators beside this repository's calls on one GPU and exit")
     args = ap.parse_args()
     if args.profile_case:
         run_profile_case(args.profile_case)
+    elif args.compare:
+        run_compare(args.compare)
     elif args.impl == "reference":
         run_reference_arm(args)
     else:
