@@ -174,7 +174,8 @@ def run_reference_arm(args):
 # DRAM read + write bytes per element of one transform launch (steady state of the rotating in-place loop below), from
 # a one-pass ncu capture of `bench.py --profile-case fwht-sweep` with the caches left alone between launches
 # (profiles/fwht_sweep_dram_bytes.md); the algorithmic figure is 4 bytes per element.
-FWHT_DRAM_BYTES_PER_ELEMENT = {}
+FWHT_DRAM_BYTES_PER_ELEMENT = {256: 3.759, 512: 3.857, 1024: 3.925, 2048: 3.958, 4096: 3.968, 8192: 3.984, 16384: 3.988,
+                               32768: 3.998}
 
 
 def time_fwht_sweep(pkg, torch, peaks, rows=16384, reps=10):
@@ -495,6 +496,7 @@ def time_host_call_cost(pkg, torch, calls=200):
     ws = torch.empty(pkg.fused_gemm_workspace_bytes(256, 256, 1024, torch.bfloat16), dtype=torch.uint8, device="cuda")
     BF16, F32 = pkg._lib.BF16, pkg._lib.F32
     cases = {
+        "ctypes_call_of_a_no_op": lambda: lib.b200ht_launch_count(),   # what the Python binding itself costs
         "fwht_trivial": lambda: lib.b200ht_fwht(tiny.data_ptr(), tiny.data_ptr(), 1, 2, BF16, 1.0, st),
         "fwht_64x1024": lambda: lib.b200ht_fwht(x.data_ptr(), x.data_ptr(), 64, 1024, BF16, 1.0 / 32, st),
         "gemv_256x4096_b4": lambda: lib.b200ht_fused_gemv(W.data_ptr(), X.data_ptr(), Y.data_ptr(), 256, 4096, 4, BF16,
