@@ -29,6 +29,7 @@ EXPORTS = (
     "b200ht_fused_gemm_scaled",
     "b200ht_fused_gemm_static",
     "b200ht_fused_gemv",
+    "b200ht_fused_gemv_max_batch",
     "b200ht_device_status",
     "b200ht_launch_count",
     "b200ht_selftest_wait_timeout",
@@ -62,6 +63,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.b200ht_fused_gemm_static.argtypes = [vp, vp, vp, i, i, i, i, i, i, f, vp]
     lib.b200ht_fused_gemv.restype = i
     lib.b200ht_fused_gemv.argtypes = [vp, vp, vp, i, i, i, i, i, f, vp]
+    lib.b200ht_fused_gemv_max_batch.restype = i
+    lib.b200ht_fused_gemv_max_batch.argtypes = [i, i]
     lib.b200ht_selftest_wait_timeout.restype = i
     lib.b200ht_selftest_wait_timeout.argtypes = [ctypes.c_uint, vp]
     lib.b200ht_launch_count.restype = ctypes.c_ulonglong

@@ -24,7 +24,7 @@ OUT = HERE / "libb200ht.so"
 OBJ_DIR = HERE / "build"
 STAMP = HERE / "libb200ht.so.sha"   # digest of the sources the library was built from
 
-SOURCES = ["api.cu", "fwht.cu", "fwht_tcgen05.cu", "fused_gemm.cu", "gemm_tcgen05.cu", "fused_gemv.cu"]
+SOURCES = ["api.cu", "fwht.cu", "fwht_tcgen05.cu", "fused_gemm.cu", "gemm_tcgen05.cu", "fused_gemv.cu", "fused_gemv_tc.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -13,10 +13,16 @@
 //         the same 8 k of H(X) for the B operand of mma.sync, so the two mma of
 //         a 32-wide k block see one consistent permutation of k.
 //   fp32: exact FFMA path (correctness cases), one warp per row.
+#include <cstdlib>
+
 #include "tc_common.cuh"
 #include "fwht_f32.cuh"
 
 namespace b200ht {
+
+int gemv_tc_cols_max(int N, int B);
+int launch_gemv_tc(const void *W, const void *X, void *Y, int M, int N, int logn, int B, int b0, int Bg, int out_dtype,
+                   float scale, cudaStream_t st);
 
 __device__ __forceinline__ uint4 ld_nc16(const void *p)
 {
@@ -804,7 +810,23 @@ int launch_gemv(const void *W, const void *X, void *Y, int M, int N, int B, int 
         }
         return 0;
     }
-    // bf16 fast path: up to 32 columns per launch
+    // bf16, 256 <= N <= 8192: the tcgen05 kernel (fused_gemv_tc.cu), all columns whose H(X) fits in shared memory per
+    // launch.  B200HT_GEMV_MMA_SYNC=1 selects the mma.sync kernels below instead (A/B comparison).
+    static const bool use_mma_sync = [] {
+        const char *e = std::getenv("B200HT_GEMV_MMA_SYNC");
+        return e && e[0] == '1';
+    }();
+    if (!use_mma_sync) {
+        if (const int cols_max = gemv_tc_cols_max(N, B)) {
+            for (int b0 = 0; b0 < B; b0 += cols_max) {
+                const int Bg = (B - b0) < cols_max ? (B - b0) : cols_max;
+                const int rc = launch_gemv_tc(W, X, Y, M, N, logn, B, b0, Bg, out_dtype, scale, st);
+                if (rc) return rc;
+            }
+            return 0;
+        }
+    }
+    // bf16, mma.sync streaming kernel: up to 32 columns per launch
     if (const int cols_max = stream_cols_max(N, B)) {
         for (int b0 = 0; b0 < B; b0 += cols_max) {
             const int Bg = (B - b0) < cols_max ? (B - b0) : cols_max;
@@ -853,4 +875,12 @@ extern "C" int b200ht_fused_gemv(const void *W, const void *X, void *Y, int M, i
     int rc = check_device();
     if (rc) return rc;
     return launch_gemv(W, X, Y, M, N, B, in_dtype, out_dtype, scale, (cudaStream_t)stream);
+}
+
+extern "C" int b200ht_fused_gemv_max_batch(int N, int in_dtype)
+{
+    using namespace b200ht;
+    if (N < 2 || N > (1 << kMaxLogN) || !is_pow2((uint64_t)N)) return 0;
+    if (in_dtype != B200HT_BF16) return 0;
+    return gemv_tc_cols_max(N, 65536);
 }

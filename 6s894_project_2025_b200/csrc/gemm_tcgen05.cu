@@ -504,6 +504,21 @@ int encode_tmap_bf16_rows_chunks(CUtensorMap *map, const void *base, uint64_t ro
     });
 }
 
+int encode_tmap_bf16_row_groups(CUtensorMap *map, const void *base, uint64_t group_rows, uint64_t groups, uint64_t cols,
+                                uint32_t box_rows, uint32_t box_chunks)
+{
+    return tmap_cached(map, TmapKey{base, groups, cols, group_rows, box_rows, box_chunks, 3, B200HT_BF16, 0},
+                       [&](EncodeTiledFn fn, CUtensorMap *m) {
+        const cuuint64_t dims[4] = {64, group_rows, groups, cols / 64};
+        const cuuint64_t strides[3] = {cols * 2, group_rows * cols * 2, 128};
+        const cuuint32_t box[4] = {64, box_rows, 1, box_chunks};
+        const cuuint32_t estr[4] = {1, 1, 1, 1};
+        return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void *>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    });
+}
+
 // Output map for the TMA-store epilogue: rows x cols of fp32 or bf16, box = 32 rows x 128 bytes, 128-byte swizzle.
 static int encode_tmap_out_2d(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint64_t ld, int dtype)
 {

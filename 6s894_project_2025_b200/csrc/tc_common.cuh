@@ -170,5 +170,10 @@ int encode_tmap_b16_2d(CUtensorMap *map, const void *base, uint64_t rows, uint64
 // Host: 3-D view [64 k][rows][cols/64] of the same matrix; box = box_rows x (64*box_chunks) elements.
 int encode_tmap_bf16_rows_chunks(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols,
                                  uint32_t box_rows, uint32_t box_chunks);
+// Host: 4-D view [64 k][group_rows][groups][cols/64] of the first groups*group_rows rows of the same matrix; box =
+// {64, box_rows, 1, box_chunks} with box_rows >= group_rows: the surplus rows of a box lie outside the second
+// dimension and are filled with zeros, so each 64-k tile in shared memory has box_rows rows.
+int encode_tmap_bf16_row_groups(CUtensorMap *map, const void *base, uint64_t group_rows, uint64_t groups, uint64_t cols,
+                                uint32_t box_rows, uint32_t box_chunks);
 
 }  // namespace b200ht

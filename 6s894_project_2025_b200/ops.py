@@ -242,8 +242,10 @@ def fused_ht_gemv(W: torch.Tensor, X: torch.Tensor, *, scale: float | None = Non
     (M, B) with b fastest — the layouts and the argument order (W, X) of
     ``fused_hadamard_gemv_kernel`` (fused_ht/fwht_gemv_fusion.cu:98-159).
     ``scale`` defaults to 1/sqrt(N); the reference uses 1.0.  Built for small
-    batches: with more than 64 columns (the reference's benchmark goes up to
-    2048, :643-653) the call is served by the fused GEMM, which reads W once.
+    batches: when the transformed columns no longer fit in shared memory beside
+    the stream of W (more than 16 columns at N = 4096, 64 at N <= 1024; the
+    reference's benchmark goes up to 2048, :643-653) the call is served by the
+    fused GEMM, which also reads W once.
     """
     if X.dtype != W.dtype or X.dtype not in (torch.float32, torch.bfloat16):
         raise RuntimeError("fused_ht_gemv: W and X must both be float32 or both bfloat16")
@@ -262,9 +264,10 @@ def fused_ht_gemv(W: torch.Tensor, X: torch.Tensor, *, scale: float | None = Non
     if scale is None:
         scale = math.sqrt(1.0 / N)
     out_dtype = out_dtype or torch.float32
-    if B > 64:
-        return fused_ht_gemm(X.t().contiguous(), W, scale=scale, out_dtype=out_dtype, out_layout="mn", out=out)
     lib = _lib.load()
+    once = int(lib.b200ht_fused_gemv_max_batch(N, _DT[W.dtype]))   # columns served by one pass over W
+    if B > 64 or (once and B > once and N >= 64):
+        return fused_ht_gemm(X.t().contiguous(), W, scale=scale, out_dtype=out_dtype, out_layout="mn", out=out)
     X = X.contiguous()
     W = W.contiguous()
     if out is None:

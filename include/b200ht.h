@@ -146,7 +146,11 @@ int b200ht_fused_gemm_scaled(const void *X, const void *W, void *C, int M, int N
  *  - The function calls no cudaMalloc/cudaFree and no allocating library
  *    routine.  Its first call on a device resolves the device address of the
  *    array (cudaGetSymbolAddress) and caches it; make that first call during
- *    set-up, before any stream capture is started.
+ *    set-up, before any stream capture is started.  The CUDA driver itself may
+ *    still load kernel code, and reserve memory for it, the first time a kernel
+ *    variant runs (each combination of in_dtype, out_dtype, out_layout and tile
+ *    shape is its own kernel): make one set-up call per combination that will
+ *    be used later, or run the process with CUDA_MODULE_LOADING=EAGER.
  *  - All calls on one device share the array, and it keeps the previous call's
  *    contents (nothing needs clearing: each call overwrites what it reads).
  *    Two calls whose kernels may run at the same time on one GPU (different
@@ -165,11 +169,12 @@ int b200ht_fused_gemm_static(const void *X, const void *W, void *C, int M, int N
  * (the reference's own benchmark calls it with B up to 2048,
  * fused_ht/fwht_gemv_fusion.cu:643-653).
  * in_dtype F32 | BF16 (W and X alike), out_dtype F32 | BF16.  For BF16 with
- * 256 <= N <= 8192 W is streamed from HBM once per group of up to 32 columns
- * (once for B <= 32 when N <= 2048, for B <= 16 at N = 4096, for B <= 8 at
- * N = 8192); other shapes use smaller column groups.  The entry is built for
- * small B: with more than 64 columns b200ht_fused_gemm (tokens = columns of
- * X) reads W once and is the faster call.
+ * 256 <= N <= 8192 the transformed X stays in shared memory as a tensor-core
+ * operand and W is streamed from HBM once per group of up to
+ * b200ht_fused_gemv_max_batch(N, B200HT_BF16) columns (64 for N <= 1024, 32 at
+ * N = 2048, 16 at N = 4096, 8 at N = 8192); other shapes use smaller column
+ * groups.  The entry is built for small B: beyond that batch
+ * b200ht_fused_gemm (tokens = columns of X) reads W once and is the faster call.
  * Argument order W, X, Y, M, N, B as in
  *   __global__ void fused_hadamard_gemv_kernel(const float* W, const float* X,
  *   float* Y, int M, int N, int B)   (fused_ht/fwht_gemv_fusion.cu:98-105; the
@@ -178,6 +183,14 @@ int b200ht_fused_gemm_static(const void *X, const void *W, void *C, int M, int N
  */
 int b200ht_fused_gemv(const void *W, const void *X, void *Y, int M, int N, int B,
                       int in_dtype, int out_dtype, float scale, void *stream);
+
+/*
+ * Largest batch B for which b200ht_fused_gemv streams W exactly once (the transformed X of all columns fits in shared
+ * memory beside the ring of W tiles); 0 when the shape takes a path without that property.  A caller with more
+ * columns should use b200ht_fused_gemm.  No counterpart in the reference, which streams W once per column at any B
+ * (fused_ht/fwht_gemv_fusion.cu:98-159).
+ */
+int b200ht_fused_gemv_max_batch(int N, int in_dtype);
 
 /*
  * Number of kernels this library has launched in the calling process so far (all entry points, all streams).

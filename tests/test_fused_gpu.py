@@ -324,3 +324,60 @@ def test_epilogue_scales(pkg, oracle, dtype, M, N, K):
         Ce = pkg.fused_ht_gemm(Xd, Wd, exact=True, row_scale=rs, token_scale=ts)
         _check(oracle, Ce.cpu().numpy(), base * rs.double().numpy()[:, None] * ts.double().numpy()[None, :], tol)
     assert pkg.device_status() == 0
+
+
+@pytest.mark.parametrize("M,N,B", [(6000, 4096, 24), (77, 4096, 40), (500, 8192, 20), (333, 2048, 70)])
+def test_gemv_c_abi_with_more_columns_than_fit_in_shared_memory(pkg, oracle, M, N, B):
+    """Straight through the C ABI with more columns than b200ht_fused_gemv_max_batch: the entry serves them in column
+    groups (W is then streamed once per group; the Python wrapper would send such a batch to the fused GEMM)."""
+    lib = pkg._lib.load()
+    assert 0 < lib.b200ht_fused_gemv_max_batch(N, pkg._lib.BF16) < B
+    g = torch.Generator().manual_seed(2000 + M + N + B)
+    W = (torch.randn(M, N, generator=g) / N ** 0.5).bfloat16().cuda()
+    X = torch.randn(N, B, generator=g).bfloat16().cuda()
+    Y = torch.empty(M, B, dtype=torch.float32, device="cuda")
+    rc = lib.b200ht_fused_gemv(W.data_ptr(), X.data_ptr(), Y.data_ptr(), M, N, B, pkg._lib.BF16, pkg._lib.F32,
+                               float(N ** -0.5), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, pkg._lib.error_string(rc)
+    assert pkg.device_status() == 0
+    ref = oracle.fused_gemv_ref(W.double().cpu().numpy(), X.double().cpu().numpy())
+    _check(oracle, Y.cpu().numpy(), ref, BF16_TOL)
+
+
+def test_gemv_max_batch_table(pkg):
+    lib = pkg._lib.load()
+    got = {n: lib.b200ht_fused_gemv_max_batch(n, pkg._lib.BF16) for n in (128, 256, 1024, 2048, 4096, 8192, 16384)}
+    assert got == {128: 0, 256: 64, 1024: 64, 2048: 32, 4096: 16, 8192: 8, 16384: 0}
+    assert lib.b200ht_fused_gemv_max_batch(4096, pkg._lib.F32) == 0
+
+
+@pytest.mark.gpu
+def test_gemv_mma_sync_kernels_agree_with_the_oracle():
+    """The mma.sync streaming kernel stays in the library for A/B comparison (B200HT_GEMV_MMA_SYNC=1, read once per
+    process): run it in a child process on a few shapes."""
+    import os
+    import subprocess
+    import sys
+    import textwrap
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    code = textwrap.dedent(f"""
+        import importlib, sys
+        sys.path.insert(0, {str(root)!r})
+        import torch
+        pkg = importlib.import_module("6s894_project_2025_b200")
+        oracle = importlib.import_module("oracle.fwht_oracle")
+        g = torch.Generator().manual_seed(5)
+        for M, N, B in ((4096, 4096, 4), (300, 1024, 8), (1000, 8192, 8), (4096, 4096, 16)):
+            W = (torch.randn(M, N, generator=g) / N ** 0.5).bfloat16()
+            X = torch.randn(N, B, generator=g).bfloat16()
+            ref = oracle.fused_gemv_ref(W.double().numpy(), X.double().numpy())
+            Y = pkg.fused_ht_gemv(W.cuda(), X.cuda()).cpu().numpy()
+            assert oracle.rel_fro(Y, ref) <= 2e-2, (M, N, B)
+        assert pkg.device_status() == 0
+        print("ok")
+    """)
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600,
+                       env=dict(os.environ, B200HT_GEMV_MMA_SYNC="1"))
+    assert r.returncode == 0 and "ok" in r.stdout, r.stdout + r.stderr
