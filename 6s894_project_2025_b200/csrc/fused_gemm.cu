@@ -5,6 +5,7 @@
 // stay L2-resident, followed on the same stream by the contraction against W.
 //   fp32 inputs: exact fp32 butterflies + FFMA GEMM (sgemm_nt_kernel, this file)
 //   bf16 inputs: 16-bit transform (fwht.cu) + tcgen05 GEMM (gemm_tcgen05.cu)
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -16,7 +17,7 @@ int launch_fwht(const void *in, void *out, uint64_t rows, uint32_t n, int dtype,
                 cudaStream_t st);
 int launch_gemm_bf16_tcgen05(const void *Y, const void *W, void *C, int M, int N, int K, int out_dtype,
                              int out_layout, cudaStream_t st, const float *row_scale = nullptr,
-                             const float *tok_scale = nullptr);
+                             const float *tok_scale = nullptr, size_t ldc = 0);
 
 // ---------------------------------------------------------------------------
 // C[m, n] = sum_k A[m, k] * Bm[n, k]   (both operands K-contiguous), fp32 FFMA.
@@ -276,13 +277,45 @@ static int fused_gemm_entry(const void *X, const void *W, void *C, int M, int N,
         return launch_fp32_tc((const float *)X, (const float *)W, C, M, N, K, scale, out_dtype, out_layout,
                               (unsigned char *)workspace + ((((size_t)N * K * 4) + 255) & ~(size_t)255), st, row_scale,
                               tok_scale);
-    rc = launch_fwht(X, workspace, (uint64_t)N, (uint32_t)K, in_dtype, scale, signs, st);
-    if (rc) return rc;
     if (in_dtype == B200HT_F32) {
+        rc = launch_fwht(X, workspace, (uint64_t)N, (uint32_t)K, in_dtype, scale, signs, st);
+        if (rc) return rc;
         return launch_sgemm((const float *)W, (const float *)workspace, C, M, N, K, out_dtype, out_layout, st, row_scale,
                             tok_scale);
     }
-    return launch_gemm_bf16_tcgen05(workspace, W, C, M, N, K, out_dtype, out_layout, st, row_scale, tok_scale);
+    // bf16.  A token range whose transformed rows would not stay in the 126 MB L2 is processed in chunks: transform
+    // of a chunk into the (one) chunk-sized head of the workspace, contraction of that chunk against all of W, next
+    // chunk.  Every kernel of the chain waits for its predecessor, so the chunk is written, read while it is still in
+    // L2, and overwritten by the next chunk before its lines are evicted: the transformed tokens do not travel to HBM
+    // and back.  B200HT_GEMM_CHUNK_MB=<MB> sets the chunk size (0: one chunk; tuning knob).
+    static const size_t chunk_bytes = [] {
+        size_t mb = 32;
+        if (const char *e = std::getenv("B200HT_GEMM_CHUNK_MB")) mb = (size_t)std::atol(e);
+        return mb << 20;
+    }();
+    const size_t row_bytes = (size_t)K * 2;
+    if (chunk_bytes == 0 || K < 64 || (size_t)N * row_bytes <= chunk_bytes + chunk_bytes / 2) {
+        rc = launch_fwht(X, workspace, (uint64_t)N, (uint32_t)K, in_dtype, scale, signs, st);
+        if (rc) return rc;
+        return launch_gemm_bf16_tcgen05(workspace, W, C, M, N, K, out_dtype, out_layout, st, row_scale, tok_scale);
+    }
+    long per = (long)(chunk_bytes / row_bytes) & ~255L;       // tokens per chunk: whole 256-token tiles
+    if (per < 256) per = 256;
+    const long nchunks = (N + per - 1) / per;
+    per = (((N + nchunks - 1) / nchunks) + 255) & ~255L;      // balanced
+    const size_t out_esz = out_dtype == B200HT_F32 ? 4 : 2;
+    for (long t0 = 0; t0 < N; t0 += per) {
+        const int nt = (int)((N - t0) < per ? (N - t0) : per);
+        rc = launch_fwht((const unsigned char *)X + (size_t)t0 * row_bytes, workspace, (uint64_t)nt, (uint32_t)K, in_dtype,
+                         scale, signs, st);
+        if (rc) return rc;
+        unsigned char *Cc = (unsigned char *)C + (out_layout == B200HT_OUT_MN ? (size_t)t0 : (size_t)t0 * M) * out_esz;
+        rc = launch_gemm_bf16_tcgen05(workspace, W, Cc, M, nt, K, out_dtype, out_layout, st, row_scale,
+                                      tok_scale ? tok_scale + t0 : nullptr,
+                                      out_layout == B200HT_OUT_MN ? (size_t)N : (size_t)M);
+        if (rc) return rc;
+    }
+    return 0;
 }
 
 extern "C" int b200ht_fused_gemm(const void *X, const void *W, void *C, int M, int N, int K, int in_dtype,

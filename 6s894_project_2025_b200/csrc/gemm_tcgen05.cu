@@ -106,25 +106,36 @@ __device__ __forceinline__ void tc_store_chunk(void *C, int M, int N, size_t ld,
     }
 }
 
-// Tile order: groups of TC_GROUP_M row blocks of W; inside a group the token
-// blocks advance slowest, so the W rows of a group (and the few token blocks
-// in flight) stay L2-resident while the whole token range streams past them.
-constexpr int TC_GROUP_M = 16;
-__device__ __forceinline__ void tc_tile_coord(int tile, int mt, int nt, int &mb, int &nb)
+// Tile order.  The tiles of one "wave" (one per SM, consecutive tile numbers) should share operand blocks, and what
+// one wave leaves in the 126 MB L2 should serve the next.
+//   order 0: groups of `group` row blocks of W; inside a group the token blocks advance slowest, so the W rows of
+//            the group stay L2-resident while the whole token range streams past them.
+//   order 1: groups of `group` token blocks; inside a group the row blocks of W advance slowest, so the tokens of
+//            the group (transformed just before, still in L2) stay resident while W streams past them once.
+struct TileOrder {
+    int group;
+    int order;
+};
+__device__ __forceinline__ void tc_tile_coord(int tile, int mt, int nt, TileOrder ord, int &mb, int &nb)
 {
-    const int per_group = TC_GROUP_M * nt;
+    const int inner_cnt = ord.order == 0 ? mt : nt;    // blocks along the grouped dimension
+    const int outer_cnt = ord.order == 0 ? nt : mt;
+    const int per_group = ord.group * outer_cnt;
     const int grp = tile / per_group;
     const int rem = tile - grp * per_group;
-    const int gsz = (mt - grp * TC_GROUP_M) < TC_GROUP_M ? (mt - grp * TC_GROUP_M) : TC_GROUP_M;
-    nb = rem / gsz;
-    mb = grp * TC_GROUP_M + (rem - nb * gsz);
+    const int left = inner_cnt - grp * ord.group;
+    const int gsz = left < ord.group ? left : ord.group;
+    const int o = rem / gsz;
+    const int i = grp * ord.group + (rem - o * gsz);
+    mb = ord.order == 0 ? i : o;
+    nb = ord.order == 0 ? o : i;
 }
 
 template <int OUT_DT, int LAYOUT, int MT>
 __global__ void __launch_bounds__(TcCfg<MT>::THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmY,
                const __grid_constant__ CUtensorMap tmC, int tma_store, void *C, int M, int N, int K, size_t ldc,
-               int ntiles_run, int pdl_mode, const float *row_scale, const float *tok_scale, int *status)
+               int ntiles_run, int pdl_mode, TileOrder ord, const float *row_scale, const float *tok_scale, int *status)
 {
     using Cfg = TcCfg<MT>;
     constexpr int STAGES = Cfg::STAGES, STAGE_BYTES = Cfg::STAGE_BYTES, NACC = Cfg::NACC;
@@ -188,7 +199,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             bool ok = true;
             for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
                 int mb, nb;
-                tc_tile_coord(tile, mt, nt, mb, nb);
+                tc_tile_coord(tile, mt, nt, ord, mb, nb);
                 const int m0 = mb * Cfg::BM, n0 = nb * TC_BN;
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int s = it % STAGES;
@@ -252,7 +263,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             const int acc = tcount % NACC;
             const uint32_t aph = (tcount / NACC) & 1u;
             int mb, nb;
-            tc_tile_coord(tile, mt, nt, mb, nb);
+            tc_tile_coord(tile, mt, nt, ord, mb, nb);
             const int m0 = mb * Cfg::BM, n0 = nb * TC_BN;
             if (!mbar_wait(tfull_bar(acc), aph, abort_flag, status)) { ok = false; break; }
             tc_fence_after();
@@ -536,7 +547,7 @@ static int encode_tmap_out_2d(CUtensorMap *map, const void *base, uint64_t rows,
 
 template <int OUT_DT, int LAYOUT, int MT>
 static int launch_tc_mt(const void *Y, const void *W, void *C, int M, int N, int K, size_t ldc, int skip_last_tiles,
-                        int pdl_mode, const float *row_scale, const float *tok_scale, cudaStream_t st)
+                        int pdl_mode, TileOrder ord, const float *row_scale, const float *tok_scale, cudaStream_t st)
 {
     using Cfg = TcCfg<MT>;
     CUtensorMap tw, ty;
@@ -558,11 +569,11 @@ static int launch_tc_mt(const void *Y, const void *W, void *C, int M, int N, int
     const int tiles = ((M + Cfg::BM - 1) / Cfg::BM) * ((N + TC_BN - 1) / TC_BN) - skip_last_tiles;
     const int grid = tiles < sm_count() ? tiles : sm_count();
     return launch_pdl(gemm_tc_kernel<OUT_DT, LAYOUT, MT>, dim3(grid), dim3(Cfg::THREADS), (size_t)Cfg::SMEM_BYTES, st,
-                      tw, ty, tc, tma_store, C, M, N, K, ldc, tiles, pdl_mode, row_scale, tok_scale, status_word_ptr());
+                      tw, ty, tc, tma_store, C, M, N, K, ldc, tiles, pdl_mode, ord, row_scale, tok_scale, status_word_ptr());
 }
 
 template <int OUT_DT, int LAYOUT>
-static int launch_tc(const void *Y, const void *W, void *C, int M, int N, int K, const float *row_scale,
+static int launch_tc(const void *Y, const void *W, void *C, int M, int N, int K, size_t ldc_arg, const float *row_scale,
                      const float *tok_scale, cudaStream_t st)
 {
     // 256-row or 128-row CTA tiles: whichever needs less time in units of a 128-row tile, counting whole waves
@@ -576,41 +587,55 @@ static int launch_tc(const void *Y, const void *W, void *C, int M, int N, int K,
         const char *e = std::getenv("B200HT_GEMM_SPLIT");
         return !(e && e[0] == '0');
     }();
-    const size_t ldc = LAYOUT == B200HT_OUT_MN ? (size_t)N : (size_t)M;
+    // B200HT_GEMM_GROUP=<blocks> and B200HT_GEMM_ORDER=0|1 override the tile order (tuning knobs).
+    static const TileOrder ord = [] {
+        TileOrder o{16, 0};
+        if (const char *e = std::getenv("B200HT_GEMM_GROUP")) {
+            const int v = std::atoi(e);
+            if (v >= 1 && v <= 1024) o.group = v;
+        }
+        if (const char *e = std::getenv("B200HT_GEMM_ORDER")) o.order = e[0] == '1' ? 1 : 0;
+        return o;
+    }();
+    const size_t ldc = ldc_arg ? ldc_arg : (LAYOUT == B200HT_OUT_MN ? (size_t)N : (size_t)M);
     const long sms = sm_count();
     const long nt = (N + TC_BN - 1) / TC_BN;
     const long mt256 = (M + 255) / 256;
     const long tiles128 = (long)((M + 127) / 128) * nt, tiles256 = mt256 * nt;
     // With 256-row tiles the last, partial wave costs a whole tile time.  When the tiles of that wave form a rectangle
-    // at the end of the tile order (rows of the last group of 16 row blocks x the last token blocks) and fit one wave
-    // as 128-row tiles, they can be computed by a second launch with 128-row tiles: half the time for the tail.
+    // at the end of the tile order (blocks of the last group x the last blocks of the other dimension) and fit one
+    // wave as 128-row tiles, they can be computed by a second launch with 128-row tiles: half the time for the tail.
+    const long inner_cnt = ord.order == 0 ? mt256 : nt, outer_cnt = ord.order == 0 ? nt : mt256;
     const long rem = tiles256 % sms;
-    const long gl = mt256 % TC_GROUP_M ? mt256 % TC_GROUP_M : TC_GROUP_M;   // row blocks in the last group
+    const long gl = inner_cnt % ord.group ? inner_cnt % ord.group : (inner_cnt < ord.group ? inner_cnt : ord.group);
     const bool can_split = allow_split && tiles256 > sms && rem > 0 && 2 * rem <= sms && (rem <= gl || rem % gl == 0) &&
-                           rem < gl * nt;
+                           rem < gl * outer_cnt;
     const double cost128 = 1.03 * (double)((tiles128 + sms - 1) / sms);
     const double cost256 = can_split ? 2.0 * (double)(tiles256 / sms) + 1.03 : 2.0 * (double)((tiles256 + sms - 1) / sms);
     const bool big = force_mt ? force_mt == 2 : (tiles256 >= sms && cost256 <= cost128);
-    if (!big) return launch_tc_mt<OUT_DT, LAYOUT, 1>(Y, W, C, M, N, K, ldc, 0, 0, row_scale, tok_scale, st);
+    if (!big) return launch_tc_mt<OUT_DT, LAYOUT, 1>(Y, W, C, M, N, K, ldc, 0, 0, ord, row_scale, tok_scale, st);
     if (can_split && !force_mt) {
-        const long cols = rem <= gl ? 1 : rem / gl;          // token blocks of the rectangle
-        const long rows = rem <= gl ? rem : gl;              // 256-row blocks of the rectangle
+        const long in_blocks = rem <= gl ? rem : gl;          // blocks of the rectangle along the grouped dimension
+        const long out_blocks = rem <= gl ? 1 : rem / gl;     // ... and along the other one
+        const long rows = ord.order == 0 ? in_blocks : out_blocks;   // 256-row blocks
+        const long cols = ord.order == 0 ? out_blocks : in_blocks;   // token blocks
         const long row_off = (mt256 - rows) * 256, tok_off = (nt - cols) * TC_BN;
-        int rc = launch_tc_mt<OUT_DT, LAYOUT, 2>(Y, W, C, M, N, K, ldc, (int)rem, 1, row_scale, tok_scale, st);
+        int rc = launch_tc_mt<OUT_DT, LAYOUT, 2>(Y, W, C, M, N, K, ldc, (int)rem, 1, ord, row_scale, tok_scale, st);
         if (rc) return rc;
         const size_t esz = OUT_DT == B200HT_F32 ? 4 : 2;
         const size_t coff = LAYOUT == B200HT_OUT_MN ? (size_t)row_off * ldc + (size_t)tok_off : (size_t)tok_off * ldc + (size_t)row_off;
         return launch_tc_mt<OUT_DT, LAYOUT, 1>((const unsigned char *)Y + (size_t)tok_off * K * 2,
                                                (const unsigned char *)W + (size_t)row_off * K * 2,
                                                (unsigned char *)C + coff * esz, (int)(M - row_off), (int)(N - tok_off), K, ldc,
-                                               0, 2, row_scale ? row_scale + row_off : nullptr,
+                                               0, 2, ord, row_scale ? row_scale + row_off : nullptr,
                                                tok_scale ? tok_scale + tok_off : nullptr, st);
     }
-    return launch_tc_mt<OUT_DT, LAYOUT, 2>(Y, W, C, M, N, K, ldc, 0, 0, row_scale, tok_scale, st);
+    return launch_tc_mt<OUT_DT, LAYOUT, 2>(Y, W, C, M, N, K, ldc, 0, 0, ord, row_scale, tok_scale, st);
 }
 
+// `ldc` = leading dimension of C in elements when C is a block of a larger matrix (0: the block is the matrix).
 int launch_gemm_bf16_tcgen05(const void *Y, const void *W, void *C, int M, int N, int K, int out_dtype,
-                             int out_layout, cudaStream_t st, const float *row_scale, const float *tok_scale)
+                             int out_layout, cudaStream_t st, const float *row_scale, const float *tok_scale, size_t ldc)
 {
     if (K < TC_BK) {
         dim3 blk(32, 8), grd((N + 31) / 32, (M + 7) / 8);
@@ -621,12 +646,12 @@ int launch_gemm_bf16_tcgen05(const void *Y, const void *W, void *C, int M, int N
     }
     if (out_dtype == B200HT_F32) {
         return out_layout == B200HT_OUT_MN
-                   ? launch_tc<B200HT_F32, B200HT_OUT_MN>(Y, W, C, M, N, K, row_scale, tok_scale, st)
-                   : launch_tc<B200HT_F32, B200HT_OUT_NM>(Y, W, C, M, N, K, row_scale, tok_scale, st);
+                   ? launch_tc<B200HT_F32, B200HT_OUT_MN>(Y, W, C, M, N, K, ldc, row_scale, tok_scale, st)
+                   : launch_tc<B200HT_F32, B200HT_OUT_NM>(Y, W, C, M, N, K, ldc, row_scale, tok_scale, st);
     }
     return out_layout == B200HT_OUT_MN
-               ? launch_tc<B200HT_BF16, B200HT_OUT_MN>(Y, W, C, M, N, K, row_scale, tok_scale, st)
-               : launch_tc<B200HT_BF16, B200HT_OUT_NM>(Y, W, C, M, N, K, row_scale, tok_scale, st);
+               ? launch_tc<B200HT_BF16, B200HT_OUT_MN>(Y, W, C, M, N, K, ldc, row_scale, tok_scale, st)
+               : launch_tc<B200HT_BF16, B200HT_OUT_NM>(Y, W, C, M, N, K, ldc, row_scale, tok_scale, st);
 }
 
 }  // namespace b200ht

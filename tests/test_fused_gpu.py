@@ -381,3 +381,58 @@ def test_gemv_mma_sync_kernels_agree_with_the_oracle():
     r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600,
                        env=dict(os.environ, B200HT_GEMV_MMA_SYNC="1"))
     assert r.returncode == 0 and "ok" in r.stdout, r.stdout + r.stderr
+
+
+@pytest.mark.parametrize("env", [{"B200HT_GEMM_CHUNK_MB": "1"}, {"B200HT_GEMM_ORDER": "1", "B200HT_GEMM_GROUP": "3"},
+                                 {"B200HT_GEMM_ORDER": "0", "B200HT_GEMM_GROUP": "5", "B200HT_GEMM_CHUNK_MB": "2"},
+                                 {"B200HT_GEMM_SPLIT": "0", "B200HT_GEMM_CHUNK_MB": "0"}])
+def test_fused_gemm_chunking_and_tile_orders_agree_bit_for_bit(pkg, oracle, tmp_path, env):
+    """The token range is processed in L2-sized chunks, the tiles of the contraction are visited in groups along rows
+    or tokens, and a partial last wave of 256-row tiles is recomputed as 128-row tiles by a second launch.  None of
+    that may change a single bit: every output element is the same K-ordered sum whatever tile holds it.  A child
+    process runs the library with the knobs set (they are read once per process) on shapes with ragged edges, more
+    than one wave and both rectangle forms of the split; the parent compares with its own default-configuration
+    result over the FULL matrix and checks that against the oracle."""
+    import os
+    import subprocess
+    import sys
+    import textwrap
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    shapes = [(4096, 2560, 64, "nm"), (2900, 3333, 512, "mn"), (6400, 6144, 128, "nm"), (9000, 5000, 64, "mn")]
+    code = textwrap.dedent(f"""
+        import importlib, sys
+        sys.path.insert(0, {str(root)!r})
+        import torch
+        pkg = importlib.import_module("6s894_project_2025_b200")
+        for i, (M, N, K, layout) in enumerate({shapes!r}):
+            g = torch.Generator().manual_seed(77 + i)
+            X = torch.randn(N, K, generator=g).bfloat16().cuda()
+            W = torch.randn(M, K, generator=g).bfloat16().cuda()
+            rs = torch.rand(M, generator=g).cuda() + 0.5
+            ts = torch.rand(N, generator=g).cuda() + 0.5
+            C = pkg.fused_ht_gemm(X, W, out_layout=layout, out_dtype=torch.bfloat16, row_scale=rs, token_scale=ts)
+            C2 = pkg.fused_ht_gemm(X, W, out_layout=layout)     # twice in a row on the stream, fp32 out
+            torch.save((C.cpu(), C2.cpu()), {str(tmp_path)!r} + f"/c{{i}}.pt")
+        assert pkg.device_status() == 0
+        print("ok")
+    """)
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=900,
+                       env=dict(os.environ, **env))
+    assert r.returncode == 0 and "ok" in r.stdout, r.stdout + r.stderr
+    for i, (M, N, K, layout) in enumerate(shapes):
+        g = torch.Generator().manual_seed(77 + i)
+        X = torch.randn(N, K, generator=g).bfloat16()
+        W = torch.randn(M, K, generator=g).bfloat16()
+        rs = torch.rand(M, generator=g) + 0.5
+        ts = torch.rand(N, generator=g) + 0.5
+        C = pkg.fused_ht_gemm(X.cuda(), W.cuda(), out_layout=layout, out_dtype=torch.bfloat16, row_scale=rs.cuda(),
+                              token_scale=ts.cuda()).cpu()
+        C2 = pkg.fused_ht_gemm(X.cuda(), W.cuda(), out_layout=layout).cpu()
+        Cc, C2c = torch.load(tmp_path / f"c{i}.pt")
+        assert torch.equal(C, Cc) and torch.equal(C2, C2c), (env, M, N, K, layout)
+        ref = oracle.fused_gemm_ref(X.double().numpy(), W.double().numpy())
+        got = C2.double().numpy() if layout == "mn" else C2.double().numpy().T
+        assert oracle.rel_fro(got, ref) <= BF16_TOL
+    assert pkg.device_status() == 0
