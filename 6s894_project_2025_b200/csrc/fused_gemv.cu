@@ -810,13 +810,14 @@ int launch_gemv(const void *W, const void *X, void *Y, int M, int N, int B, int 
         }
         return 0;
     }
-    // bf16, 256 <= N <= 8192: the tcgen05 kernel (fused_gemv_tc.cu), all columns whose H(X) fits in shared memory per
-    // launch.  B200HT_GEMV_MMA_SYNC=1 selects the mma.sync kernels below instead (A/B comparison).
-    static const bool use_mma_sync = [] {
-        const char *e = std::getenv("B200HT_GEMV_MMA_SYNC");
+    // bf16, 256 <= N <= 8192.  Two kernels cover these shapes: the mma.sync streaming kernel below (the default: it is
+    // the faster one on a B200, 8.5-9 us against 9.8-10 us at W 4096 x 4096, B <= 4) and the tcgen05 kernel of
+    // fused_gemv_tc.cu, selected with B200HT_GEMV_TCGEN05=1 (read once per process).
+    static const bool use_tcgen05 = [] {
+        const char *e = std::getenv("B200HT_GEMV_TCGEN05");
         return e && e[0] == '1';
     }();
-    if (!use_mma_sync) {
+    if (use_tcgen05) {
         if (const int cols_max = gemv_tc_cols_max(N, B)) {
             for (int b0 = 0; b0 < B; b0 += cols_max) {
                 const int Bg = (B - b0) < cols_max ? (B - b0) : cols_max;
@@ -882,5 +883,5 @@ extern "C" int b200ht_fused_gemv_max_batch(int N, int in_dtype)
     using namespace b200ht;
     if (N < 2 || N > (1 << kMaxLogN) || !is_pow2((uint64_t)N)) return 0;
     if (in_dtype != B200HT_BF16) return 0;
-    return gemv_tc_cols_max(N, 65536);
+    return stream_cols_max(N, 65536);
 }

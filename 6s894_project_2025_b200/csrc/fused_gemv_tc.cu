@@ -5,30 +5,29 @@
 // is read from HBM exactly once and H(X) never leaves the SM.
 //
 // One CTA per SM owns a contiguous range of rows of W, cut into groups of at most
-// 32 or 64 rows (ring tiles of 32 or 64 rows).  Per CTA:
+// 32 rows.  Per CTA:
 //   * W streams through a shared-memory ring by TMA.  The tensor map is a 4-D view
-//     [64 k][rows of a group][group][N/64] of W whose box holds the group's rows
-//     rounded up to 32 or 64: the missing rows are filled with zeros
-//     by the copy engine, so every 64-k tile of the ring is a whole number of
-//     1024-byte swizzle atoms and is directly a K-major A operand.  The ring's first fill is
-//     requested by sixteen lanes at once, right after every warp has issued its
-//     first loads of X.
-//   * Meanwhile all sixteen warps copy X (N x B, b fastest) into shared memory as
-//     the K-major B operand -- per 64-k chunk NU rows (one per column of X, NU = B
-//     rounded up to 8 / 16 / 32 / 64) of 128 bytes, 128-byte swizzle -- and
-//     transform the columns there in place (rot8 on 256-element chunks, fp32
-//     register butterflies for the remaining index bits).  16-byte vectors of a
-//     column stay 16-byte vectors under the swizzle, so the transform works on
-//     the operand layout directly.
-//   * Then one thread issues the MMAs.  A single product of a group's rows with 16 k would be a tiny instruction
-//     (M <= 64, N = NU), and a chain of such instructions into one accumulator runs at the latency of a dependent
-//     tcgen05.mma (about 100 cycles each, measured), not at the rate W arrives.  So one tcgen05.mma takes the tiles
-//     of CH = 128 / (rows of a tile) consecutive 64-k chunks at once as its M = 128 rows and the same chunks of
-//     H(X) as its N = CH * NU columns: the accumulator holds all CH x CH chunk pairs, of which the CH matching
-//     ones (row block j, column block j) are the wanted partial sums, and successive instructions rotate over up
-//     to four accumulators so that none waits for the one before.  tcgen05.commit hands each ring stage back to the
-//     producer thread.  Four warps drain finished accumulators with tcgen05.ld, add the accumulators and the CH
-//     diagonal blocks through shared memory and store the rows of Y; a second set of accumulators lets the next
+//     [64 k][rows of a group][group][N/64] of W whose box is 32 rows high: rows
+//     beyond the group's are filled with zeros by the copy engine, so every 64-k
+//     tile of the ring is four whole 1024-byte swizzle atoms and is directly a
+//     K-major tensor-core operand.  The ring's first fill is requested by sixteen
+//     lanes at once, right after every warp has issued its first loads of X.
+//   * Meanwhile all sixteen warps copy X (N x B, b fastest) into shared memory in
+//     operand layout -- per 64-k chunk NU rows (one per column of X, NU = B rounded
+//     up to 8 / 16 / 32 / 64) of 128 bytes, 128-byte swizzle -- and transform the
+//     columns there in place (rot8 on 256-element chunks, fp32 register
+//     butterflies for the remaining index bits).  16-byte vectors of a column
+//     stay 16-byte vectors under the swizzle, so the transform works on the
+//     operand layout directly.
+//   * Then one thread issues the MMAs.  What an instruction costs here is set by the rows it fetches from shared
+//     memory, about 0.8 cycles per row of the A operand plus some 50 cycles, whatever its N (measured: 100 cycles
+//     for M = 64, 150 for M = 128), so the operand with few rows goes on the A side and every instruction takes
+//     as much of W as an instruction can: A = H(X), 128 operand rows = the NU-row tiles of 128 / NU consecutive
+//     64-k chunks; B = the 32-row W tiles of CPN = min(8, 128 / NU) consecutive chunks, N = 32 * CPN <= 256.  The
+//     accumulator then holds every (chunk j' of H(X), chunk j of W) pair; the CPN pairs with j' = j are the wanted
+//     partial sums, the others are ignored.  32 instructions cover a row group at N = 4096.  tcgen05.commit hands
+//     each ring stage back to the producer thread.  Four warps drain a finished accumulator with tcgen05.ld, add
+//     the CPN diagonal blocks through shared memory and store the rows of Y; a second accumulator lets the next
 //     row group start meanwhile.
 // Every mbarrier wait is time-limited (B200HT_ERR_TIMEOUT in the status word).
 #include "tc_common.cuh"
@@ -37,7 +36,7 @@ namespace b200ht {
 
 constexpr int GT_WARPS = 16;
 constexpr int GT_THREADS = GT_WARPS * 32;
-constexpr int GT_MAX_GROUP_ROWS = 64;    // rows of W per ring tile: 32 or 64
+constexpr int GT_TILE_ROWS = 32;         // rows of a ring tile (a row group has at most that many rows of W)
 constexpr int GT_MAX_STAGES = 16;        // the first fill is issued by one lane per stage
 
 // Byte offset of the 16-byte vector v (elements 8v .. 8v+7) of column `col` in the B operand: 64-k chunks of NU
@@ -161,20 +160,19 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t *r)
                  : "memory");
 }
 
-// Accumulators: 4 * NU columns each (CH <= 4 chunk blocks of NU columns), NACC of them used in rotation, two such
-// sets (consecutive row groups); 2 * NACC * 4 * NU <= 512 TMEM columns.
+// Chunks of W per instruction (the B side, N = 32 * CPN) and TMEM columns: two accumulators of N columns.
 template <int NU>
 struct GtAcc {
-    static constexpr int WIDTH = 4 * NU;
-    static constexpr int NACC = 256 / WIDTH >= 4 ? 4 : (256 / WIDTH >= 1 ? 256 / WIDTH : 1);
-    static constexpr uint32_t TMEM_COLS = 2 * NACC * WIDTH < 32 ? 32u : (uint32_t)(2 * NACC * WIDTH);
+    static constexpr int CPN = 128 / NU < 8 ? 128 / NU : 8;
+    static constexpr int NMMA = GT_TILE_ROWS * CPN;
+    static constexpr uint32_t TMEM_COLS = 2 * NMMA;   // 512, 256 or 128
 };
 
 template <int NU>
 __global__ void __launch_bounds__(GT_THREADS, 1)
 gemv_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmMain, const __grid_constant__ CUtensorMap tmTail,
                     const __nv_bfloat16 *X, void *Y, int M, int N, int logn, int B, int b0, int Bg, int out_dtype,
-                    float scale, int groups_per_cta, int group_rows, int r8, int n_full_groups, int kc, int stage_bytes,
+                    float scale, int groups_per_cta, int group_rows, int n_full_groups, int kc, int stage_bytes,
                     int nstages, int *status)
 {
     extern __shared__ unsigned char smem_dyn[];
@@ -183,8 +181,8 @@ gemv_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmMain, const __grid_con
     unsigned char *gen = smem_dyn + (ring_s - smem_u32(smem_dyn));
     unsigned char *hx = gen + (size_t)nstages * stage_bytes;                      // [N/64][NU][128 bytes]
     const uint32_t hx_s = ring_s + (uint32_t)(nstages * stage_bytes);
-    float *red = (float *)(hx + (size_t)N * NU * 2);                                // [128 accumulator rows][NU]
-    unsigned char *bar_mem = (unsigned char *)(red + 128 * NU);
+    float *red = (float *)(hx + (size_t)N * NU * 2);                                // [128 accumulator rows][32]
+    unsigned char *bar_mem = (unsigned char *)(red + 128 * GT_TILE_ROWS);
     const uint32_t bar_s = smem_u32(bar_mem);
     auto full_bar = [&](int s) { return bar_s + 8u * s; };                        // TMA landed
     auto empty_bar = [&](int s) { return bar_s + 8u * (GT_MAX_STAGES + s); };     // the MMAs reading the stage are done
@@ -194,7 +192,9 @@ gemv_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmMain, const __grid_con
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
     volatile int *epi_ok = (volatile int *)(tmem_slot + 2);
     constexpr uint32_t TMEM_COLS = GtAcc<NU>::TMEM_COLS;
-    constexpr int NACC = GtAcc<NU>::NACC, ACC_W = GtAcc<NU>::WIDTH;
+    constexpr int NMMA = GtAcc<NU>::NMMA;                                  // accumulator stride in TMEM columns
+    const int cpn = (N / 64) < GtAcc<NU>::CPN ? (N / 64) : GtAcc<NU>::CPN;   // chunks of W per instruction
+    constexpr int r8 = GT_TILE_ROWS;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
@@ -203,7 +203,6 @@ gemv_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmMain, const __grid_con
     const int g_begin = blockIdx.x * groups_per_cta;
     const int ngroups = total_groups - g_begin < groups_per_cta ? (total_groups - g_begin > 0 ? total_groups - g_begin : 0)
                                                                 : groups_per_cta;
-    const int ch = 128 / r8;                // 64-k chunks per MMA: r8 (rows of a ring tile, 32 or 64) x ch = 128
     const int nchunks = (N / 64) / kc;      // ring items per row group
     const int total_items = ngroups * nchunks;
 
@@ -395,29 +394,30 @@ gemv_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmMain, const __grid_con
     if (warp == 0) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc_bf16(128, ch * NU);
-            const int steps = kc / ch;   // MMA steps (ch chunks each) per ring item
+            const uint32_t idesc = umma_idesc_bf16(128, r8 * cpn);
+            const int steps = kc / cpn;   // instruction groups (cpn chunks each) per ring item
             bool ok = true;
             for (int g = 0; g < ngroups && ok; ++g) {
                 const int slot = g & 1;
                 if (!mbar_wait(acce_bar(slot), ((uint32_t)(g >> 1) & 1u) ^ 1u, abort_flag, status)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t d_slot = tmem_base + (uint32_t)(slot * NACC * ACC_W);
-                int n_mma = 0;   // instructions issued for this group: accumulator n_mma % NACC, first use overwrites
+                const uint32_t d_tmem = tmem_base + (uint32_t)(slot * NMMA);
                 for (int ci = 0; ci < nchunks; ++ci) {
                     const int item = g * nchunks + ci;
                     const int s = item % nstages;
                     if (!mbar_wait(full_bar(s), (uint32_t)(item / nstages) & 1u, abort_flag, status)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t a_s = ring_s + (uint32_t)(s * stage_bytes);
-                    const uint32_t b_s = hx_s + (uint32_t)(ci * kc * (NU * 128));
+                    const uint32_t w_s = ring_s + (uint32_t)(s * stage_bytes);
+                    const uint32_t h_s = hx_s + (uint32_t)(ci * kc * (NU * 128));
                     for (int c = 0; c < steps; ++c) {
-                        const uint64_t adesc = umma_desc_k_sw128(a_s + (uint32_t)(c * 128 * 128));
-                        const uint64_t bdesc = umma_desc_k_sw128(b_s + (uint32_t)(c * ch * (NU * 128)));
+                        // A: 128 operand rows of H(X) from chunk ci*kc + c*cpn on (the first cpn chunks matter; the
+                        // window may run further, at the very end into the reduction buffer);
+                        // B: the cpn W tiles of the same chunks
+                        const uint64_t adesc = umma_desc_k_sw128(h_s + (uint32_t)(c * cpn * (NU * 128)));
+                        const uint64_t bdesc = umma_desc_k_sw128(w_s + (uint32_t)(c * cpn * (r8 * 128)));
 #pragma unroll
-                        for (int ks = 0; ks < 4; ++ks, ++n_mma)
-                            umma_bf16_ss(d_slot + (uint32_t)((n_mma % NACC) * ACC_W), adesc + 2 * ks, bdesc + 2 * ks, idesc,
-                                         n_mma >= NACC ? 1u : 0u);
+                        for (int ks = 0; ks < 4; ++ks)
+                            umma_bf16_ss(d_tmem, adesc + 2 * ks, bdesc + 2 * ks, idesc, (ci | c | ks) ? 1u : 0u);
                     }
                     umma_commit(empty_bar(s));
                 }
@@ -449,13 +449,14 @@ gemv_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmMain, const __grid_con
         __syncwarp();
     } else if (warp >= 4 && warp < 8) {
         // ------------------------------ epilogue ------------------------------
-        // Accumulator row L = 32 * q + lane (this warp's TMEM lanes) is row L % r8 of the group against chunk block
-        // L / r8; its wanted values are the NU columns of the same chunk block.
+        // Accumulator lane L = 32 * q + lane holds column b = L % NU of H(X) for chunk block j' = L / NU; its wanted
+        // values are the 32 accumulator columns of the same chunk block (the rows of the group), if j' < cpn.
         const int q = warp & 3;
         const int L = q * 32 + lane;
-        const int jblk = L / r8;
-        const int et = tid - 4 * 32;   // 0..127 within the epilogue warps
-        // Warp 4 waits for the accumulators and publishes the outcome; the named barrier that follows is executed by
+        const int jmine = L / NU;
+        constexpr int JPW = NU >= 32 ? 1 : 32 / NU;   // chunk blocks per warp
+        const int et = tid - 4 * 32;                  // 0..127 within the epilogue warps
+        // Warp 4 waits for the accumulator and publishes the outcome; the named barrier that follows is executed by
         // all four warps whatever the outcome, so they leave the loop together if the wait gave up.  The same
         // barrier separates the previous group's reads of `red` from this group's writes.
         for (int g = 0; g < ngroups; ++g) {
@@ -467,34 +468,37 @@ gemv_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmMain, const __grid_con
             asm volatile("bar.sync 1, 128;\n" ::: "memory");
             if (!*epi_ok) break;
             tc_fence_after();
-            uint32_t r[NU];
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(slot * NACC * ACC_W + jblk * NU);
+            uint32_t keep[32];
 #pragma unroll
-            for (int j = 0; j < NU / 8; ++j) tmem_ld8(taddr + 8 * j, r + 8 * j);
-            tmem_ld_wait();
+            for (int j = 0; j < 32; ++j) keep[j] = 0u;
+            const int jfirst = (q * 32) / NU;
 #pragma unroll
-            for (int a = 1; a < NACC; ++a) {
-                uint32_t t2[NU];
+            for (int sub = 0; sub < JPW; ++sub) {
+                const int jb = jfirst + sub;          // warp-uniform
+                if (jb < cpn) {
+                    uint32_t r[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(slot * NMMA + jb * 32), r);
+                    tmem_ld_wait();
+                    if (jb == jmine) {
 #pragma unroll
-                for (int j = 0; j < NU / 8; ++j) tmem_ld8(taddr + (uint32_t)(a * ACC_W) + 8 * j, t2 + 8 * j);
-                tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < NU; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(t2[j]));
+                        for (int j = 0; j < 32; ++j) keep[j] = r[j];
+                    }
+                }
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acce_bar(slot));
             // add the chunk blocks through shared memory and store
 #pragma unroll
-            for (int j = 0; j < NU; j += 4)
-                *(float4 *)(red + L * NU + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                                            __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            for (int j = 0; j < 32; j += 4)
+                *(float4 *)(red + L * 32 + j) = make_float4(__uint_as_float(keep[j]), __uint_as_float(keep[j + 1]),
+                                                            __uint_as_float(keep[j + 2]), __uint_as_float(keep[j + 3]));
             asm volatile("bar.sync 1, 128;\n" ::: "memory");
             const long row0 = (long)(g_begin + g) * group_rows;
             for (int idx = et; idx < group_rows * Bg; idx += 128) {
                 const int rg = idx / Bg, c = idx - rg * Bg;
                 float sum = 0.f;
-                for (int j = 0; j < ch; ++j) sum += red[(j * r8 + rg) * NU + c];
+                for (int j = 0; j < cpn; ++j) sum += red[(j * NU + c) * 32 + rg];
                 const long row = row0 + rg;
                 if (row < M) {
                     const size_t o = (size_t)row * B + b0 + c;
@@ -517,45 +521,42 @@ gemv_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmMain, const __grid_con
 // host
 // ---------------------------------------------------------------------------
 constexpr size_t kTcSmemLimit = 225 * 1024;
+constexpr size_t kTcMinRing = 48 * 1024;
 static size_t tc_fixed_smem(int N, int nu)
 {
-    return (size_t)N * nu * 2 + (size_t)128 * nu * 4 /*reduction*/ + 1024 /*alignment*/ + 8 * (2 * GT_MAX_STAGES + 4) + 64;
+    return (size_t)N * nu * 2 + (size_t)128 * GT_TILE_ROWS * 4 /*reduction*/ + 1024 /*alignment*/ + 8 * (2 * GT_MAX_STAGES + 4) + 64;
 }
 static int nu_of(int cols) { return cols <= 8 ? 8 : (cols <= 16 ? 16 : (cols <= 32 ? 32 : 64)); }
 
-// Columns per launch of the tcgen05 kernel (all of B if H(X) fits beside a ring of at least 64 KB), 0 if the shape
+// Columns per launch of the tcgen05 kernel (all of B if H(X) fits beside a ring of at least 48 KB), 0 if the shape
 // does not take it.
 int gemv_tc_cols_max(int N, int B)
 {
     if (N < 256 || N > 8192) return 0;
     int cols = B < 64 ? B : 64;
-    while (cols > 8 && tc_fixed_smem(N, nu_of(cols)) + 64 * 1024 > kTcSmemLimit) cols = nu_of(cols) / 2;
-    return tc_fixed_smem(N, nu_of(cols)) + 64 * 1024 <= kTcSmemLimit ? cols : 0;
+    while (cols > 8 && tc_fixed_smem(N, nu_of(cols)) + kTcMinRing > kTcSmemLimit) cols = nu_of(cols) / 2;
+    return tc_fixed_smem(N, nu_of(cols)) + kTcMinRing <= kTcSmemLimit ? cols : 0;
 }
 
 template <int NU>
 static int launch_gemv_tc_nu(const void *W, const void *X, void *Y, int M, int N, int logn, int B, int b0, int Bg,
                              int out_dtype, float scale, cudaStream_t st)
 {
-    // One CTA per SM, but never fewer than 8 rows per CTA.  The rows of a CTA go in equal groups of at most 32 or at
-    // most 64 rows (ring tiles of 32 or 64 rows, the rest of a tile is zero-filled and costs shared memory only):
-    // whichever pads less.
+    // One CTA per SM, but never fewer than 8 rows per CTA.  The rows of a CTA go in equal groups of at most 32 rows
+    // (the rest of a 32-row ring tile is zero-filled and costs shared memory only).
     int grid = sm_count();
     if (grid > (M + 7) / 8) grid = (M + 7) / 8;
     int rows_per_cta = (M + grid - 1) / grid;
-    const int ga = (rows_per_cta + 31) / 32, ra = (rows_per_cta + ga - 1) / ga;   // tiles of 32 rows
-    const int gb = (rows_per_cta + 63) / 64, rb = (rows_per_cta + gb - 1) / gb;   // tiles of 64 rows
-    const bool use64 = rb > 32 && 64 * ra <= 32 * rb;                             // 64 / rb <= 32 / ra
-    const int groups = use64 ? gb : ga;
-    const int group_rows = use64 ? rb : ra;
-    const int r8 = use64 ? 64 : 32;
-    const int ch = 128 / r8;
+    const int groups = (rows_per_cta + GT_TILE_ROWS - 1) / GT_TILE_ROWS;
+    const int group_rows = (rows_per_cta + groups - 1) / groups;
+    constexpr int r8 = GT_TILE_ROWS;
+    const int ch = (N / 64) < GtAcc<NU>::CPN ? (N / 64) : GtAcc<NU>::CPN;   // chunks per instruction
     rows_per_cta = groups * group_rows;
     grid = (M + rows_per_cta - 1) / rows_per_cta;
     const int n_full = M / group_rows;          // groups with all their rows; >= 1 because group_rows <= M
     const int tail_rows = M - n_full * group_rows;
-    // One TMA op = r8 x (64*kc) elements, at most 32 KB, kc a power of two dividing N/64 and a multiple of the
-    // chunks per MMA; at most 16 stages.  Take the plan that keeps most bytes in flight, and among equals the finer one.
+    // One TMA op = 32 x (64*kc) elements, at most 32 KB, kc a power of two dividing N/64 and a multiple of the
+    // chunks per instruction; at most 16 stages.  Take the plan that keeps most bytes in flight, and among equals the finer one.
     const size_t ring_room = kTcSmemLimit - tc_fixed_smem(N, NU);
     int kc = 0, stages = 0, stage_bytes = 0;
     size_t best = 0;
@@ -583,7 +584,7 @@ static int launch_gemv_tc_nu(const void *W, const void *X, void *Y, int M, int N
     rc = ensure_dyn_smem((const void *)gemv_bf16_tc_kernel<NU>, (int)smem);
     if (rc) return rc;
     return launch_pdl(gemv_bf16_tc_kernel<NU>, dim3(grid), dim3(GT_THREADS), smem, st, tmain, ttail,
-                      (const __nv_bfloat16 *)X, Y, M, N, logn, B, b0, Bg, out_dtype, scale, groups, group_rows, r8, n_full, kc,
+                      (const __nv_bfloat16 *)X, Y, M, N, logn, B, b0, Bg, out_dtype, scale, groups, group_rows, n_full, kc,
                       stage_bytes, stages, status_word_ptr());
 }
 

@@ -1,4 +1,4 @@
-// Same-box GPU comparator driver (test infrastructure, run by hand): launches the reference's fused GEMV kernels
+// Same-box GPU comparator driver (not product code, not an oracle): launches the reference's fused GEMV kernels
 //   fused_hadamard_gemv_kernel / fused_hadamard_gemv_kernel_vec <<<B, 256, N*4>>>(W, X, Y, M, N, B)
 // (fused_ht/fwht_gemv_fusion.cu:98-244, launch configuration of :383-400), compiled unmodified from a checkout of
 // the reference, on the small-batch shape: W 4096 x 4096, B = 1, 4, 16 (fp32, the only type they take; unscaled
@@ -66,8 +66,9 @@ int main()
                 for (int k = 0; k < N; ++k) acc += (double)hW[(size_t)row * N + k] * v[k];
                 maxrel = fmax(maxrel, fabs(acc - hY[(size_t)row * B]) / fmax(1e-9, fabs(acc)));
             }
-            printf("B=%2d %-6s %10.1f us  %8.1f GB/s of fp32 W  max rel err %.2e (4 rows)\n", B, vec ? "vec" : "plain",
-                   ms * 1000.0, (double)M * N * 4 / ms / 1e6, maxrel);
+            printf("RESULT case=%s shape=gemv m=%d n=%d batch=%d dtype=float32 runs=%d per_iter_ms=%.6f total_ms=%.4f max_rel_err=%.2e\n",
+                   vec ? "fused_hadamard_gemv_kernel_vec" : "fused_hadamard_gemv_kernel", M, N, B, reps * NW, ms,
+                   ms * reps * NW, maxrel);
         }
     }
     return 0;

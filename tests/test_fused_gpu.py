@@ -326,7 +326,7 @@ def test_epilogue_scales(pkg, oracle, dtype, M, N, K):
     assert pkg.device_status() == 0
 
 
-@pytest.mark.parametrize("M,N,B", [(6000, 4096, 24), (77, 4096, 40), (500, 8192, 20), (333, 2048, 70)])
+@pytest.mark.parametrize("M,N,B", [(6000, 4096, 24), (77, 4096, 40), (500, 8192, 20), (333, 2048, 70), (100, 512, 50)])
 def test_gemv_c_abi_with_more_columns_than_fit_in_shared_memory(pkg, oracle, M, N, B):
     """Straight through the C ABI with more columns than b200ht_fused_gemv_max_batch: the entry serves them in column
     groups (W is then streamed once per group; the Python wrapper would send such a batch to the fused GEMM)."""
@@ -347,14 +347,14 @@ def test_gemv_c_abi_with_more_columns_than_fit_in_shared_memory(pkg, oracle, M, 
 def test_gemv_max_batch_table(pkg):
     lib = pkg._lib.load()
     got = {n: lib.b200ht_fused_gemv_max_batch(n, pkg._lib.BF16) for n in (128, 256, 1024, 2048, 4096, 8192, 16384)}
-    assert got == {128: 0, 256: 64, 1024: 64, 2048: 32, 4096: 16, 8192: 8, 16384: 0}
+    assert got == {128: 0, 256: 32, 1024: 32, 2048: 32, 4096: 16, 8192: 8, 16384: 0}
     assert lib.b200ht_fused_gemv_max_batch(4096, pkg._lib.F32) == 0
 
 
-@pytest.mark.gpu
-def test_gemv_mma_sync_kernels_agree_with_the_oracle():
-    """The mma.sync streaming kernel stays in the library for A/B comparison (B200HT_GEMV_MMA_SYNC=1, read once per
-    process): run it in a child process on a few shapes."""
+def test_gemv_tcgen05_kernel_agrees_with_the_oracle():
+    """The tcgen05 GEMV kernel (B200HT_GEMV_TCGEN05=1, read once per process) in a child process: every copy-in
+    variant of X, 8 / 16 / 32 / 64 operand rows, one and several row groups per CTA, ragged last rows, column
+    groups, both output types."""
     import os
     import subprocess
     import sys
@@ -368,18 +368,28 @@ def test_gemv_mma_sync_kernels_agree_with_the_oracle():
         import torch
         pkg = importlib.import_module("6s894_project_2025_b200")
         oracle = importlib.import_module("oracle.fwht_oracle")
+        lib = pkg._lib.load()
         g = torch.Generator().manual_seed(5)
-        for M, N, B in ((4096, 4096, 4), (300, 1024, 8), (1000, 8192, 8), (4096, 4096, 16)):
+        shapes = ((4096, 4096, 4), (300, 1024, 8), (1000, 8192, 8), (4096, 4096, 16), (4096, 256, 2), (4741, 512, 12),
+                  (10000, 256, 1), (9000, 4096, 16), (8, 8192, 4), (29, 1024, 32), (333, 1024, 64), (77, 4096, 40),
+                  (28672, 8192, 3))
+        for M, N, B in shapes:
             W = (torch.randn(M, N, generator=g) / N ** 0.5).bfloat16()
             X = torch.randn(N, B, generator=g).bfloat16()
             ref = oracle.fused_gemv_ref(W.double().numpy(), X.double().numpy())
-            Y = pkg.fused_ht_gemv(W.cuda(), X.cuda()).cpu().numpy()
-            assert oracle.rel_fro(Y, ref) <= 2e-2, (M, N, B)
+            Wd, Xd = W.cuda(), X.cuda()
+            for odt, code in ((torch.float32, pkg._lib.F32), (torch.bfloat16, pkg._lib.BF16)):
+                Y = torch.empty(M, B, dtype=odt, device="cuda")
+                rc = lib.b200ht_fused_gemv(Wd.data_ptr(), Xd.data_ptr(), Y.data_ptr(), M, N, B, pkg._lib.BF16, code,
+                                           float(N ** -0.5), torch.cuda.current_stream().cuda_stream)
+                assert rc == 0, (M, N, B, rc)
+                got = Y.float().cpu().numpy()
+                assert oracle.rel_fro(got, ref) <= 2e-2 and oracle.rel_max(got, ref) <= 2e-2, (M, N, B)
         assert pkg.device_status() == 0
         print("ok")
     """)
-    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600,
-                       env=dict(os.environ, B200HT_GEMV_MMA_SYNC="1"))
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=900,
+                       env=dict(os.environ, B200HT_GEMV_TCGEN05="1"))
     assert r.returncode == 0 and "ok" in r.stdout, r.stdout + r.stderr
 
 
