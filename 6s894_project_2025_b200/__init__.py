@@ -11,7 +11,15 @@ from .ops import (  # noqa: F401
     fused_ht_gemv,
     hadamard_transform,
 )
-from .partition import gather_result, gather_rows, row_range, shard_rows, shard_tokens, token_range  # noqa: F401
+from .partition import (  # noqa: F401
+    RowShardedGemv,
+    gather_result,
+    gather_rows,
+    row_range,
+    shard_rows,
+    shard_tokens,
+    token_range,
+)
 from . import torchlib  # noqa: F401  (registers torch.ops.b200ht.*)
 
 __all__ = [
@@ -27,4 +35,5 @@ __all__ = [
     "row_range",
     "shard_rows",
     "gather_rows",
+    "RowShardedGemv",
 ]

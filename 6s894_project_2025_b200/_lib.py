@@ -30,6 +30,10 @@ EXPORTS = (
     "b200ht_fused_gemm_static",
     "b200ht_fused_gemv",
     "b200ht_fused_gemv_max_batch",
+    "b200ht_fused_gemv_peers",
+    "b200ht_ipc_export",
+    "b200ht_ipc_open",
+    "b200ht_ipc_close",
     "b200ht_device_status",
     "b200ht_launch_count",
     "b200ht_selftest_wait_timeout",
@@ -65,6 +69,15 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.b200ht_fused_gemv.argtypes = [vp, vp, vp, i, i, i, i, i, f, vp]
     lib.b200ht_fused_gemv_max_batch.restype = i
     lib.b200ht_fused_gemv_max_batch.argtypes = [i, i]
+    lib.b200ht_fused_gemv_peers.restype = i
+    lib.b200ht_fused_gemv_peers.argtypes = [vp, vp, vp, i, i, i, i, i, f, i, ctypes.POINTER(vp), ctypes.POINTER(vp), vp, vp,
+                                            i, i, ctypes.c_uint, vp]
+    lib.b200ht_ipc_export.restype = i
+    lib.b200ht_ipc_export.argtypes = [vp, ctypes.c_char_p, ctypes.POINTER(ctypes.c_ulonglong)]
+    lib.b200ht_ipc_open.restype = i
+    lib.b200ht_ipc_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]
+    lib.b200ht_ipc_close.restype = i
+    lib.b200ht_ipc_close.argtypes = [vp]
     lib.b200ht_selftest_wait_timeout.restype = i
     lib.b200ht_selftest_wait_timeout.argtypes = [ctypes.c_uint, vp]
     lib.b200ht_launch_count.restype = ctypes.c_ulonglong

@@ -14,6 +14,7 @@
 //         a 32-wide k block see one consistent permutation of k.
 //   fp32: exact FFMA path (correctness cases), one warp per row.
 #include <cstdlib>
+#include <cstring>
 
 #include "tc_common.cuh"
 #include "fwht_f32.cuh"
@@ -273,11 +274,22 @@ __device__ __forceinline__ uint32_t lds32(uint32_t saddr)
     return v;
 }
 
+// Row-sharded GEMV across GPUs: besides its own Y the kernel writes every result into the Y buffers of up to seven
+// peer GPUs (plain stores through peer-mapped pointers, no multicast) and, once all CTAs of the launch have done so,
+// bumps this rank's arrival counter on every peer.  n = 0: single-GPU call.
+struct PeerOut {
+    int n;
+    unsigned char *y[7];        // the peers' Y buffers, offset to this rank's first row
+    unsigned int *arrived[7];   // this rank's arrival counter on each peer
+    unsigned int *local_count;  // CTAs of this launch that have finished (self-resetting)
+};
+
 template <int NT>
 __global__ void __launch_bounds__(GV_THREADS, 1)
 gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bfloat16 *X, void *Y, int M, int N,
                         int logn, int B, int b0, int Bg, int out_dtype, float scale, int rows_per_cta,
-                        int group_rows, int kc, int stage_bytes, int nstages, int red_in_ring, int *status)
+                        int group_rows, int kc, int stage_bytes, int nstages, int red_in_ring, int *status,
+                        const PeerOut po)
 {
     extern __shared__ unsigned char smem_dyn[];
     // ring first (1024-byte aligned stages for the 128-byte swizzle), then H(X), reduction buffer, barriers
@@ -602,9 +614,26 @@ gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bflo
 #pragma unroll
             for (int w = 0; w < 8; ++w) sum += red[((size_t)w * 32 + r) * RC + c];
             const int row = grp_row0 + r;
-            if (r < group_rows && row < row_end) store_out(Y, (size_t)row * B + b0 + c, sum, out_dtype);
+            if (r < group_rows && row < row_end) {
+                store_out(Y, (size_t)row * B + b0 + c, sum, out_dtype);
+                for (int p = 0; p < po.n; ++p) store_out(po.y[p], (size_t)row * B + b0 + c, sum, out_dtype);
+            }
         }
         __syncthreads();
+    }
+    if (po.n) {
+        // Publish: every thread's peer stores are made visible system-wide, then the last CTA of the launch to get
+        // here bumps this rank's counter on every peer (a peer that sees the count sees all rows of this launch).
+        __threadfence_system();
+        __syncthreads();
+        if (tid == 0) {
+            const unsigned int done = atomicAdd(po.local_count, 1u) + 1u;
+            if (done == gridDim.x) {
+                atomicExch(po.local_count, 0u);
+                __threadfence_system();
+                for (int p = 0; p < po.n; ++p) atomicAdd_system(po.arrived[p], 1u);
+            }
+        }
     }
 }
 
@@ -714,7 +743,7 @@ static int stream_cols_max(int N, int B)
 
 template <int NT>
 static int launch_stream_nt(const void *W, const void *X, void *Y, int M, int N, int logn, int B, int b0, int Bg,
-                            int out_dtype, float scale, cudaStream_t st)
+                            int out_dtype, float scale, cudaStream_t st, const PeerOut &po)
 {
     // one CTA per SM, but never fewer than 8 rows per CTA
     int grid = sm_count();
@@ -757,17 +786,17 @@ static int launch_stream_nt(const void *W, const void *X, void *Y, int M, int N,
     if (rc) return rc;
     return launch_pdl(gemv_bf16_stream_kernel<NT>, dim3(grid), dim3(GV_THREADS), smem, st, tw,
                       (const __nv_bfloat16 *)X, Y, M, N, logn, B, b0, Bg, out_dtype, scale, rows_per_cta, group_rows, kc,
-                      stage_bytes, stages, red_in_ring ? 1 : 0, status_word_ptr());
+                      stage_bytes, stages, red_in_ring ? 1 : 0, status_word_ptr(), po);
 }
 
 static int launch_stream(const void *W, const void *X, void *Y, int M, int N, int logn, int B, int b0, int Bg,
-                         int out_dtype, float scale, cudaStream_t st)
+                         int out_dtype, float scale, cudaStream_t st, const PeerOut &po = PeerOut{})
 {
     switch ((Bg + 7) / 8) {
-    case 1: return launch_stream_nt<1>(W, X, Y, M, N, logn, B, b0, Bg, out_dtype, scale, st);
-    case 2: return launch_stream_nt<2>(W, X, Y, M, N, logn, B, b0, Bg, out_dtype, scale, st);
-    case 3: return launch_stream_nt<3>(W, X, Y, M, N, logn, B, b0, Bg, out_dtype, scale, st);
-    case 4: return launch_stream_nt<4>(W, X, Y, M, N, logn, B, b0, Bg, out_dtype, scale, st);
+    case 1: return launch_stream_nt<1>(W, X, Y, M, N, logn, B, b0, Bg, out_dtype, scale, st, po);
+    case 2: return launch_stream_nt<2>(W, X, Y, M, N, logn, B, b0, Bg, out_dtype, scale, st, po);
+    case 3: return launch_stream_nt<3>(W, X, Y, M, N, logn, B, b0, Bg, out_dtype, scale, st, po);
+    case 4: return launch_stream_nt<4>(W, X, Y, M, N, logn, B, b0, Bg, out_dtype, scale, st, po);
     }
     return B200HT_ERR_SIZE;
 }
@@ -876,6 +905,98 @@ extern "C" int b200ht_fused_gemv(const void *W, const void *X, void *Y, int M, i
     int rc = check_device();
     if (rc) return rc;
     return launch_gemv(W, X, Y, M, N, B, in_dtype, out_dtype, scale, (cudaStream_t)stream);
+}
+
+namespace b200ht {
+
+// Waits (time-limited, about one second) until every other rank's arrival counter in this GPU's counter array has
+// reached `target`, i.e. until all rows of the current call have landed in this GPU's Y.  One lane per rank.  On
+// expiry the status word gets B200HT_ERR_TIMEOUT and the kernel returns: nothing hangs when a peer never arrives.
+__global__ void gemv_peer_wait_kernel(const unsigned int *arrived, unsigned int target, int world, int rank, int *status)
+{
+    pdl_launch_dependents();
+    pdl_wait();   // the local GEMV of this call is complete
+    const int s = threadIdx.x;
+    if (s >= world || s == rank) return;
+    const uint64_t t0 = global_ns();
+    while (true) {
+        unsigned int seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(arrived + s) : "memory");
+        if ((int)(seen - target) >= 0) return;
+        if (global_ns() - t0 > 1000000000ull) {
+            if (status) atomicExch(status, B200HT_ERR_TIMEOUT);
+            return;
+        }
+    }
+}
+
+}  // namespace b200ht
+
+extern "C" int b200ht_fused_gemv_peers(const void *W, const void *X, void *Y, int M, int N, int B, int in_dtype, int out_dtype,
+                                       float scale, int n_peers, void *const *peer_y, unsigned int *const *peer_arrived,
+                                       unsigned int *local_count, const unsigned int *local_arrived, int world, int rank,
+                                       unsigned int target, void *stream)
+{
+    using namespace b200ht;
+    if (in_dtype != B200HT_BF16) return B200HT_ERR_DTYPE;
+    if (out_dtype != B200HT_F32 && out_dtype != B200HT_BF16) return B200HT_ERR_DTYPE;
+    if (N < 256 || N > 8192 || !is_pow2((uint64_t)N)) return B200HT_ERR_SIZE;
+    if (M < 1 || B < 1 || B > stream_cols_max(N, B)) return B200HT_ERR_SIZE;
+    if (n_peers < 0 || n_peers > 7 || world < 1 || world > 8 || rank < 0 || rank >= world) return B200HT_ERR_SIZE;
+    if (!W || !X || !Y || !local_count || !local_arrived || (n_peers && (!peer_y || !peer_arrived))) return B200HT_ERR_NULL;
+    // Y points into the middle of a result buffer (this rank's first row): element alignment is all it needs
+    if (!aligned16(W) || !aligned16(X) || ((uintptr_t)Y & 3u)) return B200HT_ERR_ALIGN;
+    int rc = check_device();
+    if (rc) return rc;
+    PeerOut po{};
+    po.n = n_peers;
+    for (int p = 0; p < n_peers; ++p) {
+        if (!peer_y[p] || !peer_arrived[p]) return B200HT_ERR_NULL;
+        po.y[p] = (unsigned char *)peer_y[p];
+        po.arrived[p] = peer_arrived[p];
+    }
+    po.local_count = local_count;
+    cudaStream_t st = (cudaStream_t)stream;
+    rc = launch_stream(W, X, Y, M, N, ilog2((uint32_t)N), B, 0, B, out_dtype, scale, st, po);
+    if (rc) return rc;
+    return launch_pdl(gemv_peer_wait_kernel, dim3(1), dim3(32), 0, st, local_arrived, target, world, rank, status_word_ptr());
+}
+
+// Inter-process mapping of device buffers (one process per GPU): export a handle for a buffer inside a cudaMalloc
+// allocation, open a peer's handle.  Thin wrappers over the CUDA IPC calls so that host code needs no CUDA binding.
+extern "C" int b200ht_ipc_export(const void *ptr, void *handle64, unsigned long long *offset)
+{
+    if (!ptr || !handle64 || !offset) return B200HT_ERR_NULL;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    CUdeviceptr base = 0;
+    size_t size = 0;
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    typedef CUresult (*RangeFn)(CUdeviceptr *, size_t *, CUdeviceptr);
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess || !fn)
+        return (int)cudaErrorNotSupported;
+    if (((RangeFn)fn)(&base, &size, (CUdeviceptr)ptr) != CUDA_SUCCESS) return (int)cudaErrorInvalidValue;
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, (void *)base);
+    if (e != cudaSuccess) return (int)e;
+    memcpy(handle64, &h, 64);
+    *offset = (unsigned long long)((CUdeviceptr)ptr - base);
+    return 0;
+}
+
+extern "C" int b200ht_ipc_open(const void *handle64, void **base)
+{
+    if (!handle64 || !base) return B200HT_ERR_NULL;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    return (int)cudaIpcOpenMemHandle(base, h, cudaIpcMemLazyEnablePeerAccess);
+}
+
+extern "C" int b200ht_ipc_close(void *base)
+{
+    if (!base) return B200HT_ERR_NULL;
+    return (int)cudaIpcCloseMemHandle(base);
 }
 
 extern "C" int b200ht_fused_gemv_max_batch(int N, int in_dtype)

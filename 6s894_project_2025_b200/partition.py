@@ -90,3 +90,152 @@ def gather_rows(Y_local: torch.Tensor, n_rows: int, group=None) -> torch.Tensor:
     world = dist.get_world_size(group)
     sizes = [row_range(n_rows, r, world) for r in range(world)]
     return _gather_row_blocks(Y_local.contiguous(), sizes, group)
+
+
+class RowShardedGemv:
+    """Small-batch ``Y = W . H(X)`` with the rows of W split over the ranks of one node, the exchange done by the
+    kernel's own stores.
+
+    Every rank keeps ``shard_rows(W)`` and the same X.  The GEMV kernel writes its rows of Y into its own result
+    buffer and, through peer-mapped pointers, into every other rank's; a per-rank arrival counter tells a rank when
+    all rows of a call have landed (``b200ht_fused_gemv_peers``).  There is no collective on the path: at W 4096 x
+    4096 an NCCL all-gather of the 64 KB result costs several times the kernel.
+
+    Set-up (once): each rank allocates one exchange buffer -- two result buffers used alternately plus the counters
+    -- exports it (CUDA IPC), the handles go round with ``all_gather_object`` and every rank maps the others'.
+    ``__call__`` returns a view of the result buffer of this call; it stays valid until the call after next.  All
+    ranks must make the same sequence of calls.  bf16, 256 <= N <= 8192, B <= ``max_batch``.
+    """
+
+    def __init__(self, W_local: torch.Tensor, n_rows: int, max_batch: int, *, out_dtype: torch.dtype = torch.float32,
+                 group=None, backend=None):
+        import torch.distributed as dist
+
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.W = W_local.contiguous()
+        self.n_rows = int(n_rows)
+        self.N = int(W_local.shape[1])
+        self.max_batch = int(max_batch)
+        self.out_dtype = out_dtype
+        self.row_begin, self.row_end = row_range(self.n_rows, self.rank, self.world)
+        if int(W_local.shape[0]) != self.row_end - self.row_begin:
+            raise RuntimeError("RowShardedGemv: W_local does not hold this rank's rows (see shard_rows)")
+        self.calls = 0
+        esz = 4 if out_dtype == torch.float32 else 2
+        self.y_bytes = (self.n_rows * self.max_batch * esz + 255) & ~255
+        self.backend = backend if backend is not None else _IpcBackend(W_local.device)
+        # exchange buffer: [counters: 256 bytes][result buffer 0][result buffer 1]
+        self.buf = self.backend.allocate(256 + 2 * self.y_bytes)
+        handle = self.backend.export(self.buf)
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle, group=group)
+        # base address of every rank's exchange buffer as seen from this GPU (own buffer: its own address)
+        self.bases = [self.backend.address(self.buf) if r == self.rank else self.backend.open(handles[r])
+                      for r in range(self.world)]
+        self.peers = [r for r in range(self.world) if r != self.rank]
+        dist.barrier(group=group)   # every rank has zeroed and mapped its buffers before the first call
+
+    # layout of the exchange buffer
+    def _arrived(self, base: int, src_rank: int) -> int:
+        return base + 4 * src_rank             # arrival counter of rank src_rank
+    def _local_count(self, base: int) -> int:
+        return base + 128                      # kernel scratch word
+    def _rows(self, base: int, parity: int, row: int, batch: int, esz: int) -> int:
+        return base + 256 + parity * self.y_bytes + row * batch * esz
+
+    def plan(self, batch: int) -> dict:
+        """Addresses and counter target of the NEXT call (also what the host-side tests check)."""
+        if not (1 <= batch <= self.max_batch):
+            raise RuntimeError(f"RowShardedGemv: batch must be in [1, {self.max_batch}]")
+        esz = 4 if self.out_dtype == torch.float32 else 2
+        parity = self.calls & 1
+        mine = self.bases[self.rank]
+        return {
+            "parity": parity,
+            "target": self.calls + 1,
+            "y_local": self._rows(mine, parity, self.row_begin, batch, esz),
+            "peer_y": [self._rows(self.bases[r], parity, self.row_begin, batch, esz) for r in self.peers],
+            "peer_arrived": [self._arrived(self.bases[r], self.rank) for r in self.peers],
+            "local_count": self._local_count(mine),
+            "local_arrived": self._arrived(mine, 0),
+            "y_full": self._rows(mine, parity, 0, batch, esz),
+        }
+
+    def __call__(self, X: torch.Tensor, *, scale: float | None = None) -> torch.Tensor:
+        if X.dim() == 1:
+            X = X[:, None]
+        batch = int(X.shape[1])
+        p = self.plan(batch)
+        self.backend.launch(self, X.contiguous(), batch, p, scale)
+        self.calls += 1
+        return self.backend.view(self.buf, p["y_full"] - self.bases[self.rank], (self.n_rows, batch), self.out_dtype)
+
+    def close(self) -> None:
+        for r in self.peers:
+            self.backend.close(self.bases[r])
+        self.peers = []
+
+
+class _IpcBackend:
+    """CUDA side of RowShardedGemv: device buffers through torch, mapping through the library's IPC wrappers."""
+
+    def __init__(self, device):
+        from . import _lib
+        self.device = device
+        self._lib = _lib
+        self.lib = _lib.load()
+        self._opened = {}
+
+    def allocate(self, nbytes: int) -> torch.Tensor:
+        # a private cudaMalloc block (IPC handles cover whole allocations): bypass the caching allocator's pooling
+        # by asking for a block larger than its small-allocation pools hand out piecemeal
+        t = torch.zeros(max(nbytes, 2 << 20), dtype=torch.uint8, device=self.device)
+        torch.cuda.synchronize(self.device)
+        return t
+
+    def address(self, buf: torch.Tensor) -> int:
+        return int(buf.data_ptr())
+
+    def export(self, buf: torch.Tensor):
+        import ctypes
+        h = ctypes.create_string_buffer(64)
+        off = ctypes.c_ulonglong(0)
+        with torch.cuda.device(self.device):
+            self._lib.check(self.lib.b200ht_ipc_export(buf.data_ptr(), h, ctypes.byref(off)), "b200ht_ipc_export")
+        return (bytes(h.raw), int(off.value))
+
+    def open(self, handle) -> int:
+        import ctypes
+        raw, off = handle
+        base = ctypes.c_void_p(0)
+        with torch.cuda.device(self.device):
+            self._lib.check(self.lib.b200ht_ipc_open(raw, ctypes.byref(base)), "b200ht_ipc_open")
+        self._opened[int(base.value) + off] = int(base.value)
+        return int(base.value) + off
+
+    def close(self, addr: int) -> None:
+        base = self._opened.pop(addr, None)
+        if base is not None:
+            self.lib.b200ht_ipc_close(base)
+
+    def launch(self, op: "RowShardedGemv", X: torch.Tensor, batch: int, p: dict, scale) -> None:
+        import ctypes
+        import math
+        n = len(p["peer_y"])
+        vp = ctypes.c_void_p
+        peer_y = (vp * max(n, 1))(*p["peer_y"])
+        peer_arrived = (vp * max(n, 1))(*p["peer_arrived"])
+        dt = {torch.float32: self._lib.F32, torch.bfloat16: self._lib.BF16}
+        sc = math.sqrt(1.0 / op.N) if scale is None else scale
+        with torch.cuda.device(self.device):
+            rc = self.lib.b200ht_fused_gemv_peers(
+                op.W.data_ptr(), X.data_ptr(), p["y_local"], op.row_end - op.row_begin, op.N, batch, dt[op.W.dtype],
+                dt[op.out_dtype], float(sc), n, peer_y, peer_arrived, p["local_count"], p["local_arrived"], op.world,
+                op.rank, p["target"], int(torch.cuda.current_stream(self.device).cuda_stream))
+        self._lib.check(rc, "b200ht_fused_gemv_peers")
+
+    def view(self, buf: torch.Tensor, offset: int, shape, dtype) -> torch.Tensor:
+        n = shape[0] * shape[1] * (4 if dtype == torch.float32 else 2)
+        return buf[offset: offset + n].view(dtype).view(shape)

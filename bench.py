@@ -700,8 +700,15 @@ def run_profile_case(case: str):
         K, M, N = (8192, 8192, 4096) if case == "gemm" else (K_DIM, M_DIM, N_TOKENS)
         W = (torch.randn(M, K, generator=g, device="cuda") / math.sqrt(K)).bfloat16()
         X = torch.randn(N, K, generator=g, device="cuda").bfloat16()
-        for _ in range(4):
+        for _ in range(3):
             C = pkg.fused_ht_gemm(X, W, out_layout="nm", out_dtype=torch.bfloat16)
+        # the fourth call is bracketed for the profiler: `ncu --profile-from-start off` then captures the kernels of
+        # exactly one fused call (transform and contraction launches alike), however many launches a call makes
+        torch.cuda.synchronize()
+        torch.cuda.cudart().cudaProfilerStart()
+        C = pkg.fused_ht_gemm(X, W, out_layout="nm", out_dtype=torch.bfloat16)
+        torch.cuda.synchronize()
+        torch.cuda.cudart().cudaProfilerStop()
         print("gemm case done", float(C.float().abs().mean()))
     elif case == "c3":      # fused W.H(X) at K=1024, 4096 tokens, M=4096, bf16 in, fp32 M x N out; rotating inputs
         K, M, N = 1024, 4096, 4096

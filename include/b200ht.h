@@ -192,6 +192,41 @@ int b200ht_fused_gemv(const void *W, const void *X, void *Y, int M, int N, int B
 int b200ht_fused_gemv_max_batch(int N, int in_dtype);
 
 /*
+ * Row-sharded small-batch GEMV across the GPUs of one node (one process per GPU).  Every rank keeps M rows of W (its
+ * shard) and the same X; the kernel writes its M x B results into its own Y and, through peer-mapped pointers, into
+ * the Y buffers of the other ranks, so that after the call every rank holds all rows: the exchange is part of the
+ * kernel's stores, not a separate collective.  No counterpart in the reference, which is single-GPU.
+ *   Y             this rank's rows inside its own full result buffer (16-byte aligned)
+ *   peer_y[p]     the same position inside peer p's full result buffer (n_peers <= 7 pointers valid on this GPU,
+ *                 e.g. from b200ht_ipc_open)
+ *   peer_arrived[p]  address, in peer p's memory, of the 32-bit arrival counter that belongs to THIS rank
+ *   local_count   a zero-initialised 32-bit word in this GPU's memory (scratch of the kernel, left at zero)
+ *   local_arrived this GPU's array of `world` arrival counters (zero-initialised once; entry `rank` is unused)
+ *   target        number of calls made so far on this exchange, this one included: all ranks call in lockstep
+ * After the GEMV kernel a one-warp kernel waits, for at most one second, until every other rank's counter has reached
+ * `target`; work enqueued behind the call sees the complete Y.  If a peer never arrives the wait gives up, the status
+ * word (b200ht_device_status) reports B200HT_ERR_TIMEOUT and nothing hangs.  A rank must not start call k + 2 before
+ * its consumers of call k's result are enqueued: alternate between two result buffers (the Python wrapper does).
+ * BF16 inputs, 256 <= N <= 8192, B <= b200ht_fused_gemv_max_batch(N, B200HT_BF16); other shapes return
+ * B200HT_ERR_SIZE (gather the shards with a collective instead).
+ */
+int b200ht_fused_gemv_peers(const void *W, const void *X, void *Y, int M, int N, int B, int in_dtype,
+                            int out_dtype, float scale, int n_peers, void *const *peer_y,
+                            unsigned int *const *peer_arrived, unsigned int *local_count,
+                            const unsigned int *local_arrived, int world, int rank, unsigned int target,
+                            void *stream);
+
+/*
+ * Inter-process mapping of device buffers for b200ht_fused_gemv_peers: b200ht_ipc_export writes a 64-byte handle for
+ * the cudaMalloc allocation that contains `ptr` and the offset of `ptr` inside it; b200ht_ipc_open maps a handle
+ * received from another process (peer access is enabled on demand) and returns the mapped base address;
+ * b200ht_ipc_close unmaps it.  Set-up calls, not for the hot path.  No counterpart in the reference.
+ */
+int b200ht_ipc_export(const void *ptr, void *handle64, unsigned long long *offset);
+int b200ht_ipc_open(const void *handle64, void **base);
+int b200ht_ipc_close(void *base);
+
+/*
  * Number of kernels this library has launched in the calling process so far (all entry points, all streams).
  * A benchmark reads it before and after a timed region to report its launch count.  No counterpart in the reference.
  */

@@ -171,3 +171,63 @@ def test_two_rank_gloo_row_sharded_gemv(tmp_path):
         capture_output=True, text=True, env=env, timeout=300)
     assert r.returncode == 0, r.stdout + r.stderr
     assert r.stdout.count("ok") == 2
+
+
+def test_two_rank_gloo_peer_store_gemv_bookkeeping(tmp_path):
+    """Host side of the peer-store row-sharded GEMV, two gloo ranks on the CPU with a stand-in for the CUDA side:
+    the handle exchange gives every rank the other ranks' buffers (never its own as a peer), this rank's rows land at
+    the same offset in every buffer, the arrival counter a rank bumps on a peer is the peer's slot for THAT rank,
+    the counter target grows by one per call and the two result buffers alternate."""
+    script = tmp_path / "worker.py"
+    script.write_text(textwrap.dedent(f"""
+        import importlib, sys
+        sys.path.insert(0, {str(ROOT)!r})
+        import torch, torch.distributed as dist
+        pkg = importlib.import_module("6s894_project_2025_b200")
+        dist.init_process_group("gloo")
+        rank, world = dist.get_rank(), dist.get_world_size()
+
+        class Fake:
+            launches = []
+            def allocate(self, nbytes): self.nbytes = nbytes; return torch.zeros(nbytes, dtype=torch.uint8)
+            def address(self, buf): return 1000000 * (rank + 1)
+            def export(self, buf): return ("handle-of", rank)
+            def open(self, handle): assert handle[0] == "handle-of"; return 1000000 * (handle[1] + 1)
+            def close(self, addr): pass
+            def launch(self, op, X, batch, plan, scale): Fake.launches.append(plan)
+            def view(self, buf, offset, shape, dtype):
+                n = shape[0] * shape[1] * 4
+                return buf[offset: offset + n].view(dtype).view(shape)
+
+        M, N, B = 11, 256, 3                      # 11 rows over 2 ranks: 6 + 5
+        a, b = pkg.row_range(M, rank, world)
+        W = torch.zeros(b - a, N, dtype=torch.bfloat16)
+        op = pkg.RowShardedGemv(W, M, 4, backend=Fake())
+        other = 1 - rank
+        assert op.peers == [other]
+        for call in range(3):
+            y = op(torch.zeros(N, B, dtype=torch.bfloat16))
+            plan = Fake.launches[-1]
+            assert y.shape == (M, B)
+            assert plan["target"] == call + 1 and plan["parity"] == call % 2
+            mine, peer = 1000000 * (rank + 1), 1000000 * (other + 1)
+            row_off = 256 + (call % 2) * op.y_bytes + a * B * 4
+            assert plan["y_local"] == mine + row_off and plan["peer_y"] == [peer + row_off]
+            assert plan["peer_arrived"] == [peer + 4 * rank]          # my counter in the peer's array
+            assert plan["local_arrived"] == mine and plan["local_count"] == mine + 128
+            assert plan["y_full"] == mine + 256 + (call % 2) * op.y_bytes
+        try:
+            op(torch.zeros(N, 5, dtype=torch.bfloat16))
+            raise SystemExit("batch beyond max_batch was accepted")
+        except RuntimeError:
+            pass
+        dist.destroy_process_group()
+        print("rank", rank, "ok")
+    """))
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="1")
+    r = subprocess.run(
+        [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+         "--master-addr", "127.0.0.1", "--master-port", "29619", str(script)],
+        capture_output=True, text=True, env=env, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert r.stdout.count("ok") == 2

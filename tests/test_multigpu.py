@@ -80,3 +80,42 @@ def test_two_gpu_row_sharded_gemv(tmp_path):
          "--master-addr", "127.0.0.1", "--master-port", "29645", str(script)],
         capture_output=True, text=True, env=env, timeout=600)
     assert r.returncode == 0 and r.stdout.count("ok") == 2, r.stdout + r.stderr
+
+
+@pytest.mark.gpu
+def test_two_gpu_row_sharded_gemv_with_peer_stores(tmp_path):
+    """The same split with the exchange inside the kernel: every GPU stores its rows of Y into both result buffers
+    through peer-mapped pointers and a counter per rank says when a call is complete.  Several calls back to back
+    (the two result buffers alternate), ragged row split, both output types; compared with the single-GPU call."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    script = tmp_path / "worker.py"
+    script.write_text(textwrap.dedent(f"""
+        import importlib, os, sys
+        sys.path.insert(0, {str(ROOT)!r})
+        import torch, torch.distributed as dist
+        pkg = importlib.import_module("6s894_project_2025_b200")
+        rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"])
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+        g = torch.Generator().manual_seed(9)
+        for M, N, odt in ((4096, 4096, torch.float32), (4097, 1024, torch.bfloat16)):
+            W = (torch.randn(M, N, generator=g) / N ** 0.5).bfloat16().cuda()
+            op = pkg.RowShardedGemv(pkg.shard_rows(W, rank, world).contiguous(), M, 16, out_dtype=odt)
+            for B in (1, 4, 16, 3):
+                X = torch.randn(N, B, generator=g).bfloat16().cuda()
+                got = op(X).clone()
+                full = pkg.fused_ht_gemv(W, X, out_dtype=odt)
+                err = float((got.float() - full.float()).norm() / full.float().norm())
+                assert err < (1e-5 if odt == torch.float32 else 1e-2), f"peer-store result differs: {{err}}"
+            op.close()
+        assert pkg.device_status() == 0
+        dist.barrier(); dist.destroy_process_group()
+        print("rank", rank, "ok")
+    """))
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0")
+    r = subprocess.run(
+        [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+         "--master-addr", "127.0.0.1", "--master-port", "29646", str(script)],
+        capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0 and r.stdout.count("ok") == 2, r.stdout + r.stderr
