@@ -249,4 +249,30 @@ __device__ __forceinline__ void st_stream(uint4 *p, const uint4 &v)
                  : "memory");
 }
 
+// L2 eviction-priority policies for accesses that carry a cache hint: `evict_first` for data that streams through
+// once, `evict_last` for data that should stay resident.
+__device__ __forceinline__ uint64_t l2_policy_evict_first()
+{
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last()
+{
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;\n" : "=l"(p));
+    return p;
+}
+// 16-byte result store: as a stream (policy 0), or with the given L2 policy.
+__device__ __forceinline__ void st_out(uint4 *p, const uint4 &v, uint64_t policy)
+{
+    if (policy == 0) {
+        st_stream(p, v);
+    } else {
+        asm volatile("st.global.L2::cache_hint.v4.u32 [%0], {%1,%2,%3,%4}, %5;\n" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
+                     "r"(v.w), "l"(policy)
+                     : "memory");
+    }
+}
+
 }  // namespace b200ht

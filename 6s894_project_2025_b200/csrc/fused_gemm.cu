@@ -14,7 +14,7 @@ namespace b200ht {
 
 int launch_fwht_f32_split(const float *in, __nv_bfloat16 *split, uint64_t rows, uint32_t n, float scale, cudaStream_t st);
 int launch_fwht(const void *in, void *out, uint64_t rows, uint32_t n, int dtype, float scale, const void *signs,
-                cudaStream_t st);
+                cudaStream_t st, int keep_out = 0);
 int launch_gemm_bf16_tcgen05(const void *Y, const void *W, void *C, int M, int N, int K, int out_dtype,
                              int out_layout, cudaStream_t st, const float *row_scale = nullptr,
                              const float *tok_scale = nullptr, size_t ldc = 0);
@@ -295,7 +295,7 @@ static int fused_gemm_entry(const void *X, const void *W, void *C, int M, int N,
     }();
     const size_t row_bytes = (size_t)K * 2;
     if (chunk_bytes == 0 || K < 64 || (size_t)N * row_bytes <= chunk_bytes + chunk_bytes / 2) {
-        rc = launch_fwht(X, workspace, (uint64_t)N, (uint32_t)K, in_dtype, scale, signs, st);
+        rc = launch_fwht(X, workspace, (uint64_t)N, (uint32_t)K, in_dtype, scale, signs, st, 1);
         if (rc) return rc;
         return launch_gemm_bf16_tcgen05(workspace, W, C, M, N, K, out_dtype, out_layout, st, row_scale, tok_scale);
     }
@@ -307,7 +307,7 @@ static int fused_gemm_entry(const void *X, const void *W, void *C, int M, int N,
     for (long t0 = 0; t0 < N; t0 += per) {
         const int nt = (int)((N - t0) < per ? (N - t0) : per);
         rc = launch_fwht((const unsigned char *)X + (size_t)t0 * row_bytes, workspace, (uint64_t)nt, (uint32_t)K, in_dtype,
-                         scale, signs, st);
+                         scale, signs, st, 1);
         if (rc) return rc;
         unsigned char *Cc = (unsigned char *)C + (out_layout == B200HT_OUT_MN ? (size_t)t0 : (size_t)t0 * M) * out_esz;
         rc = launch_gemm_bf16_tcgen05(workspace, W, Cc, M, nt, K, out_dtype, out_layout, st, row_scale,

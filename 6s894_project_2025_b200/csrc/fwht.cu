@@ -47,7 +47,7 @@ static int tc_min_logn()
 // ---------------------------------------------------------------------------
 template <int DT, int LOGN, bool SG>
 __global__ void __launch_bounds__(256) fwht_reg_kernel(const uint4 *in, uint4 *out, uint64_t total_vec,
-                                                       float mult, const uint4 *signs)
+                                                       float mult, const uint4 *signs, int keep)
 {
     constexpr int P = LOGN < 8 ? LOGN : 8;
     constexpr int CPR = LOGN > 8 ? (1 << (LOGN - 8)) : 1;  // chunks per row
@@ -56,6 +56,7 @@ __global__ void __launch_bounds__(256) fwht_reg_kernel(const uint4 *in, uint4 *o
     // drains, and wait here until everything before this kernel has completed and is visible.
     pdl_launch_dependents();
     pdl_wait();
+    const uint64_t keep_policy = keep ? l2_policy_evict_last() : 0;   // 0: streaming stores
     const int lane = threadIdx.x & 31;
     const uint64_t warp = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const uint64_t first = warp * (uint64_t)(GRP * 32);
@@ -105,7 +106,7 @@ __global__ void __launch_bounds__(256) fwht_reg_kernel(const uint4 *in, uint4 *o
             r.y = pack2<DT>(o[g][2] * mult, o[g][3] * mult);
             r.z = pack2<DT>(o[g][4] * mult, o[g][5] * mult);
             r.w = pack2<DT>(o[g][6] * mult, o[g][7] * mult);
-            st_stream(out + idx, r);
+            st_out(out + idx, r, keep_policy);
         }
     }
 }
@@ -134,13 +135,14 @@ struct SmemCfg {
 
 template <int DT, int LOGN, bool SG>
 __global__ void __launch_bounds__(SmemCfg<LOGN>::NW * 32) fwht_smem_kernel(const uint4 *in, uint4 *out, uint64_t rows,
-                                                        float mult, const uint4 *signs)
+                                                        float mult, const uint4 *signs, int keep)
 {
     using Cfg = SmemCfg<LOGN>;
     constexpr int Q = Cfg::Q, CPR = Cfg::CPR, NW = Cfg::NW;
     extern __shared__ uint4 sm[];
     pdl_launch_dependents();
     pdl_wait();
+    const uint64_t keep_policy = keep ? l2_policy_evict_last() : 0;   // 0: streaming stores
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const uint64_t row0 = (uint64_t)blockIdx.x * Cfg::SLAB_ROWS;
@@ -249,12 +251,12 @@ __global__ void __launch_bounds__(SmemCfg<LOGN>::NW * 32) fwht_smem_kernel(const
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const int c = c0 + u * CPI + cl;
-                if (c < chunks_here) st_stream(gout + c * 32 + v0, r[u]);
+                if (c < chunks_here) st_out(gout + c * 32 + v0, r[u], keep_policy);
             }
         }
     } else {
         __syncthreads();
-        for (int c = warp; c < chunks_here; c += NW) st_stream(gout + c * 32 + lane, sm[c * 33 + lane]);
+        for (int c = warp; c < chunks_here; c += NW) st_out(gout + c * 32 + lane, sm[c * 33 + lane], keep_policy);
     }
 }
 
@@ -335,7 +337,7 @@ __global__ void __launch_bounds__(256) fwht_f32_kernel(const float *in, float *o
 // host side
 // ---------------------------------------------------------------------------
 template <int DT, int LOGN>
-static int launch_reg(const void *in, void *out, uint64_t rows, float scale, const void *signs, cudaStream_t st)
+static int launch_reg(const void *in, void *out, uint64_t rows, float scale, const void *signs, cudaStream_t st, int keep)
 {
     constexpr int P = LOGN < 8 ? LOGN : 8;
     constexpr int CPR = LOGN > 8 ? (1 << (LOGN - 8)) : 1;
@@ -349,13 +351,13 @@ static int launch_reg(const void *in, void *out, uint64_t rows, float scale, con
     // of back-to-back launches overlap (the kernel itself waits for its predecessors before touching memory)
     if (signs)
         return launch_pdl(fwht_reg_kernel<DT, LOGN, true>, dim3((unsigned)blocks), dim3(256), 0, st,
-                          (const uint4 *)in, (uint4 *)out, total_vec, scale / f, (const uint4 *)signs);
+                          (const uint4 *)in, (uint4 *)out, total_vec, scale / f, (const uint4 *)signs, keep);
     return launch_pdl(fwht_reg_kernel<DT, LOGN, false>, dim3((unsigned)blocks), dim3(256), 0, st, (const uint4 *)in,
-                      (uint4 *)out, total_vec, scale / f, (const uint4 *)nullptr);
+                      (uint4 *)out, total_vec, scale / f, (const uint4 *)nullptr, keep);
 }
 
 template <int DT, int LOGN>
-static int launch_smem(const void *in, void *out, uint64_t rows, float scale, const void *signs, cudaStream_t st)
+static int launch_smem(const void *in, void *out, uint64_t rows, float scale, const void *signs, cudaStream_t st, int keep)
 {
     using Cfg = SmemCfg<LOGN>;
     const uint64_t blocks = (rows + Cfg::SLAB_ROWS - 1) / Cfg::SLAB_ROWS;
@@ -364,13 +366,13 @@ static int launch_smem(const void *in, void *out, uint64_t rows, float scale, co
         const int rc = ensure_dyn_smem((const void *)kernel, Cfg::SMEM_BYTES);
         if (rc) return rc;
         return launch_pdl(kernel, dim3((unsigned)blocks), dim3(Cfg::NW * 32), (size_t)Cfg::SMEM_BYTES, st,
-                          (const uint4 *)in, (uint4 *)out, rows, scale * 64.0f, (const uint4 *)signs);
+                          (const uint4 *)in, (uint4 *)out, rows, scale * 64.0f, (const uint4 *)signs, keep);
     };
     return signs ? go(fwht_smem_kernel<DT, LOGN, true>) : go(fwht_smem_kernel<DT, LOGN, false>);
 }
 
 template <int DT>
-static int launch_b16(const void *in, void *out, uint64_t rows, int logn, float scale, const void *signs,
+static int launch_b16(const void *in, void *out, uint64_t rows, int logn, float scale, const void *signs, int keep,
                       cudaStream_t st)
 {
     switch (logn) {
@@ -383,19 +385,19 @@ static int launch_b16(const void *in, void *out, uint64_t rows, int logn, float 
                                                               1 << logn, scale, (const uint16_t *)signs);
         return (int)cudaGetLastError();
     }
-    case 3: return launch_reg<DT, 3>(in, out, rows, scale, signs, st);
-    case 4: return launch_reg<DT, 4>(in, out, rows, scale, signs, st);
-    case 5: return launch_reg<DT, 5>(in, out, rows, scale, signs, st);
-    case 6: return launch_reg<DT, 6>(in, out, rows, scale, signs, st);
-    case 7: return launch_reg<DT, 7>(in, out, rows, scale, signs, st);
-    case 8: return launch_reg<DT, 8>(in, out, rows, scale, signs, st);
-    case 9: return launch_reg<DT, 9>(in, out, rows, scale, signs, st);
-    case 10: return launch_reg<DT, 10>(in, out, rows, scale, signs, st);
-    case 11: return launch_reg<DT, 11>(in, out, rows, scale, signs, st);
-    case 12: return launch_smem<DT, 12>(in, out, rows, scale, signs, st);
-    case 13: return launch_smem<DT, 13>(in, out, rows, scale, signs, st);
-    case 14: return launch_smem<DT, 14>(in, out, rows, scale, signs, st);
-    case 15: return launch_smem<DT, 15>(in, out, rows, scale, signs, st);
+    case 3: return launch_reg<DT, 3>(in, out, rows, scale, signs, st, keep);
+    case 4: return launch_reg<DT, 4>(in, out, rows, scale, signs, st, keep);
+    case 5: return launch_reg<DT, 5>(in, out, rows, scale, signs, st, keep);
+    case 6: return launch_reg<DT, 6>(in, out, rows, scale, signs, st, keep);
+    case 7: return launch_reg<DT, 7>(in, out, rows, scale, signs, st, keep);
+    case 8: return launch_reg<DT, 8>(in, out, rows, scale, signs, st, keep);
+    case 9: return launch_reg<DT, 9>(in, out, rows, scale, signs, st, keep);
+    case 10: return launch_reg<DT, 10>(in, out, rows, scale, signs, st, keep);
+    case 11: return launch_reg<DT, 11>(in, out, rows, scale, signs, st, keep);
+    case 12: return launch_smem<DT, 12>(in, out, rows, scale, signs, st, keep);
+    case 13: return launch_smem<DT, 13>(in, out, rows, scale, signs, st, keep);
+    case 14: return launch_smem<DT, 14>(in, out, rows, scale, signs, st, keep);
+    case 15: return launch_smem<DT, 15>(in, out, rows, scale, signs, st, keep);
     }
     return B200HT_ERR_SIZE;
 }
@@ -422,8 +424,10 @@ int launch_fwht_f32_split(const float *in, __nv_bfloat16 *split, uint64_t rows, 
     return launch_fwht_f32(in, nullptr, rows, ilog2(n), scale, st, split);
 }
 
+// keep_out != 0: the result is about to be read again (by the contraction of the fused GEMM): store it with the L2
+// eviction priority `evict_last` instead of as a stream.
 int launch_fwht(const void *in, void *out, uint64_t rows, uint32_t n, int dtype, float scale, const void *signs,
-                cudaStream_t st)
+                cudaStream_t st, int keep_out)
 {
     const int logn = ilog2(n);
     if (dtype == B200HT_F32 && signs) return B200HT_ERR_DTYPE;  // the +-1 diagonal is implemented for 16-bit data
@@ -437,8 +441,8 @@ int launch_fwht(const void *in, void *out, uint64_t rows, uint32_t n, int dtype,
     }();
     if (logn >= kTcMinLogN && !use_mma_sync && !signs && ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 127u) == 0)
         return launch_fwht_tc(in, out, rows, logn, dtype, scale, st);
-    if (dtype == B200HT_BF16) return launch_b16<B200HT_BF16>(in, out, rows, logn, scale, signs, st);
-    return launch_b16<B200HT_F16>(in, out, rows, logn, scale, signs, st);
+    if (dtype == B200HT_BF16) return launch_b16<B200HT_BF16>(in, out, rows, logn, scale, signs, keep_out, st);
+    return launch_b16<B200HT_F16>(in, out, rows, logn, scale, signs, keep_out, st);
 }
 
 }  // namespace b200ht
@@ -462,7 +466,7 @@ static int fwht_entry(const void *in, void *out, uint64_t rows, uint32_t n, int 
     }
     int rc = check_device();
     if (rc) return rc;
-    return launch_fwht(in, out, rows, n, dtype, scale, signs, (cudaStream_t)stream);
+    return launch_fwht(in, out, rows, n, dtype, scale, signs, (cudaStream_t)stream, 0);
 }
 
 extern "C" int b200ht_fwht(const void *in, void *out, uint64_t rows, uint32_t n, int dtype, float scale,

@@ -289,35 +289,54 @@ def time_gemv(pkg, torch, peaks, reps=20):
 
 
 def time_gemv_rows(pkg, torch, dist, rank, world, reps=20):
-    """Row-sharded small-batch GEMV (world > 1): every rank keeps M/world rows of W, computes its rows of Y and an
-    NCCL all-gather of M x B values assembles Y.  Timed per call including the all-gather; 8 rotating copies of the
-    W shard.  B = 4; W 4096 x 4096 (the C4 shape) and 28672 x 8192 (the C5 weight)."""
+    """Row-sharded small-batch GEMV (world > 1): every rank keeps M/world rows of W, computes its rows of Y and stores
+    them into every rank's result buffer through peer-mapped pointers (RowShardedGemv: no collective; a counter per
+    rank tells when a call is complete).  Timed per call, 8 rotating copies of the W shard, B = 4; W 4096 x 4096 (the
+    C4 shape) and 28672 x 8192 (the C5 weight).  `parity`: rank 0 compares the assembled Y of one call with the
+    single-GPU call on the full W (same seeded data on every rank).  `nccl_ms` is the same split with an NCCL
+    all-gather of Y after a plain GEMV, for comparison."""
     out = {}
-    g = torch.Generator(device="cuda").manual_seed(6)
     for M, N in ((4096, 4096), (28672, 8192)):
-        a, b = pkg.row_range(M, rank, world)
-        Ws = [(torch.randn(b - a, N, generator=g, device="cuda") / math.sqrt(N)).bfloat16() for _ in range(8)]
+        g = torch.Generator(device="cuda").manual_seed(6)       # same W and X on every rank
+        W_full = (torch.randn(M, N, generator=g, device="cuda") / math.sqrt(N)).bfloat16()
         X = torch.randn(N, 4, generator=g, device="cuda").bfloat16()
-
-        def call(Wt):
-            return pkg.gather_rows(pkg.fused_ht_gemv(Wt, X), M)
-
-        for Wt in Ws[:3]:
-            call(Wt)
+        a, b = pkg.row_range(M, rank, world)
+        Ws = [W_full[a:b].clone() if i == 0 else (torch.randn(b - a, N, generator=g, device="cuda") / math.sqrt(N)).bfloat16()
+              for i in range(8)]
+        ops = [pkg.RowShardedGemv(Wt, M, 4) for Wt in Ws]
+        got = ops[0](X).clone()
         torch.cuda.synchronize()
-        dist.barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(reps):
-            for Wt in Ws:
-                call(Wt)
-        e1.record()
-        torch.cuda.synchronize()
-        t = torch.tensor([e0.elapsed_time(e1) / (reps * len(Ws))], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-        out[f"{M}x{N}"] = {"ms": ms, "gbs_all_gpus": M * N * 2 / (ms * 1e-3) / 1e9, "rows_per_gpu": b - a}
-        del Ws
+        ref = pkg.fused_ht_gemv(W_full, X)
+        err = float((got - ref).norm() / ref.norm())
+        parity = torch.tensor([1 if err < 1e-5 else 0], device="cuda")
+        dist.all_reduce(parity, op=dist.ReduceOp.MIN)
+        del W_full
+
+        def timed(call):
+            for i in range(3):
+                call(i)
+            torch.cuda.synchronize()
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                for i in range(len(Ws)):
+                    call(i)
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) / (reps * len(Ws))], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+
+        ms = timed(lambda i: ops[i](X))
+        nccl_ms = timed(lambda i: pkg.gather_rows(pkg.fused_ht_gemv(Ws[i], X), M))
+        status = pkg.device_status()
+        out[f"{M}x{N}"] = {"ms": ms, "gbs_all_gpus": M * N * 2 / (ms * 1e-3) / 1e9, "rows_per_gpu": b - a,
+                           "parity": bool(parity.item()) and status == 0, "rel_err_vs_one_gpu": err,
+                           "nccl_all_gather_ms": nccl_ms, "exchange": "peer stores + arrival counters"}
+        for op in ops:
+            op.close()
+        del Ws, ops
     return out
 
 

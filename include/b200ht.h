@@ -171,7 +171,7 @@ int b200ht_fused_gemm_static(const void *X, const void *W, void *C, int M, int N
  * in_dtype F32 | BF16 (W and X alike), out_dtype F32 | BF16.  For BF16 with
  * 256 <= N <= 8192 the transformed X stays in shared memory and W is streamed
  * from HBM once per group of up to b200ht_fused_gemv_max_batch(N, B200HT_BF16)
- * columns (32 for N <= 2048, 16 at N = 4096, 8 at N = 8192); other shapes use
+ * columns (32 for N <= 1024, 24 at N = 2048, 16 at N = 4096, 8 at N = 8192); other shapes use
  * smaller column groups.  The entry is built for small B: beyond that batch
  * b200ht_fused_gemm (tokens = columns of X) reads W once and is the faster call.
  * Argument order W, X, Y, M, N, B as in

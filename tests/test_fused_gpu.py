@@ -347,7 +347,7 @@ def test_gemv_c_abi_with_more_columns_than_fit_in_shared_memory(pkg, oracle, M, 
 def test_gemv_max_batch_table(pkg):
     lib = pkg._lib.load()
     got = {n: lib.b200ht_fused_gemv_max_batch(n, pkg._lib.BF16) for n in (128, 256, 1024, 2048, 4096, 8192, 16384)}
-    assert got == {128: 0, 256: 32, 1024: 32, 2048: 32, 4096: 16, 8192: 8, 16384: 0}
+    assert got == {128: 0, 256: 32, 1024: 32, 2048: 24, 4096: 16, 8192: 8, 16384: 0}
     assert lib.b200ht_fused_gemv_max_batch(4096, pkg._lib.F32) == 0
 
 
