@@ -115,7 +115,6 @@ __device__ __forceinline__ void tc_store_chunk(void *C, int M, int N, size_t ld,
 struct TileOrder {
     int group;
     int order;
-    int hints;   // 1: the TMA loads carry L2 eviction priorities (see the producer warp)
 };
 __device__ __forceinline__ void tc_tile_coord(int tile, int mt, int nt, TileOrder ord, int &mb, int &nb)
 {
@@ -198,11 +197,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            // L2 priorities: the operand of the grouped dimension is the one a group keeps using (order 1: the token
-            // chunk that was transformed just before), the other one streams past it
-            const uint64_t keep = l2_policy_evict_last(), stream = l2_policy_evict_first();
-            const uint64_t pol_w = ord.hints ? (ord.order == 0 ? keep : stream) : 0;
-            const uint64_t pol_y = ord.hints ? (ord.order == 0 ? stream : keep) : 0;
             for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
                 int mb, nb;
                 tc_tile_coord(tile, mt, nt, ord, mb, nb);
@@ -213,13 +207,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, status)) { ok = false; break; }
                     mbar_expect_tx(full_bar(s), STAGE_BYTES);
                     const uint32_t sa = base + s * STAGE_BYTES;
-                    if (ord.hints) {
-                        tma_load_2d_hint(sa, &tmW, kb * TC_BK, m0, full_bar(s), pol_w);
-                        tma_load_2d_hint(sa + Cfg::A_BYTES, &tmY, kb * TC_BK, n0, full_bar(s), pol_y);
-                    } else {
-                        tma_load_2d(sa, &tmW, kb * TC_BK, m0, full_bar(s));
-                        tma_load_2d(sa + Cfg::A_BYTES, &tmY, kb * TC_BK, n0, full_bar(s));
-                    }
+                    tma_load_2d(sa, &tmW, kb * TC_BK, m0, full_bar(s));
+                    tma_load_2d(sa + Cfg::A_BYTES, &tmY, kb * TC_BK, n0, full_bar(s));
                 }
             }
             if (!ok) {
@@ -599,16 +588,16 @@ static int launch_tc(const void *Y, const void *W, void *C, int M, int N, int K,
         return !(e && e[0] == '0');
     }();
     // Default: groups of 8 token blocks (2048 tokens: one 32 MB chunk of transformed tokens at K = 8192), the order
-    // with the least DRAM traffic measured on the K = 8192, M = 28672 shape.  B200HT_GEMM_GROUP=<blocks>,
-    // B200HT_GEMM_ORDER=0|1 and B200HT_GEMM_L2HINT=0|1 override it (tuning knobs).
+    // with the least DRAM traffic measured on the K = 8192, M = 28672 shape (L2 eviction hints on the TMA loads were
+    // tried on top of it and raised the traffic).  B200HT_GEMM_GROUP=<blocks> and B200HT_GEMM_ORDER=0|1 override it
+    // (tuning knobs).
     static const TileOrder ord = [] {
-        TileOrder o{8, 1, 0};
+        TileOrder o{8, 1};
         if (const char *e = std::getenv("B200HT_GEMM_GROUP")) {
             const int v = std::atoi(e);
             if (v >= 1 && v <= 1024) o.group = v;
         }
         if (const char *e = std::getenv("B200HT_GEMM_ORDER")) o.order = e[0] == '1' ? 1 : 0;
-        if (const char *e = std::getenv("B200HT_GEMM_L2HINT")) o.hints = e[0] == '1' ? 1 : 0;
         return o;
     }();
     const size_t ldc = ldc_arg ? ldc_arg : (LAYOUT == B200HT_OUT_MN ? (size_t)N : (size_t)M);

@@ -674,10 +674,12 @@ def run_gpu_arm(args):
                        "out": "bf16 token-major"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak,
-                         # DRAM read + write bytes of one full-size GEMM launch on one GPU, from a one-pass ncu capture
-                         # of `bench.py --profile-case gemm-full` (dram__bytes_read.sum + dram__bytes_write.sum);
-                         # scaled by the token share of a rank
-                         "traffic": 6.906e9 * n_local / N_TOKENS, "traffic_unit": "B/launch",
+                         # DRAM read + write bytes of the contraction kernels of one full-size fused call on one GPU
+                         # (8 token chunks: 8 launches with 256-row tiles + 8 tail launches), from a one-pass ncu capture
+                         # of `bench.py --profile-case gemm-full` with the caches left alone between launches
+                         # (profiles/gemm_tc_kernel_fused_k8192.md); scaled by the token share of a rank
+                         "traffic": 5.509e9 * n_local / N_TOKENS, "traffic_unit": "B/fused call",
+                         "algorithmic_bytes": (M_DIM * K_DIM * 2 + n_local * K_DIM * 2 + n_local * M_DIM * 2),
                          "peak_source": f"{peaks['source']} sustained cuBLAS bf16 (burst {peaks['bf16_tflops']})",
                          "frac_of_burst": achieved / peaks["bf16_tflops"]},
             "roofline_fwht": {"bound": "hbm", "achieved": worst_fwht["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
