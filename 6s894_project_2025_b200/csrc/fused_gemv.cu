@@ -945,7 +945,7 @@ extern "C" int b200ht_fused_gemv_peers(const void *W, const void *X, void *Y, in
     if (n_peers < 0 || n_peers > 7 || world < 1 || world > 8 || rank < 0 || rank >= world) return B200HT_ERR_SIZE;
     if (!W || !X || !Y || !local_count || !local_arrived || (n_peers && (!peer_y || !peer_arrived))) return B200HT_ERR_NULL;
     // Y points into the middle of a result buffer (this rank's first row): element alignment is all it needs
-    if (!aligned16(W) || !aligned16(X) || ((uintptr_t)Y & 3u)) return B200HT_ERR_ALIGN;
+    if (!aligned16(W) || !aligned16(X) || ((uintptr_t)Y & (out_dtype == B200HT_F32 ? 3u : 1u))) return B200HT_ERR_ALIGN;
     int rc = check_device();
     if (rc) return rc;
     PeerOut po{};
