@@ -282,6 +282,9 @@ struct PeerOut {
     unsigned char *y[7];        // the peers' Y buffers, offset to this rank's first row
     unsigned int *arrived[7];   // this rank's arrival counter on each peer
     unsigned int *local_count;  // CTAs of this launch that have finished (self-resetting)
+    const unsigned int *local_arrived;   // this GPU's array of arrival counters, one per rank
+    unsigned int target;        // value the other ranks' counters reach when their rows of this call have landed
+    int world, rank;
 };
 
 template <int NT>
@@ -622,9 +625,12 @@ gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bflo
         __syncthreads();
     }
     if (po.n) {
-        // Publish: every thread's peer stores are made visible system-wide, then the last CTA of the launch to get
-        // here bumps this rank's counter on every peer (a peer that sees the count sees all rows of this launch).
-        __threadfence_system();
+        // Publish: the threads that stored make their peer stores visible system-wide; the last CTA of the launch to
+        // get here bumps this rank's counter on every peer (a peer that sees the count sees all rows of this launch)
+        // and then waits, for at most a second, until the other ranks' counters on THIS GPU have reached the call's
+        // target: when the kernel is complete, so is Y.  If a peer never arrives the wait gives up with
+        // B200HT_ERR_TIMEOUT in the status word; nothing hangs.
+        if (tid < 32 * Bg && ngroups > 0) __threadfence_system();   // the threads of the store loops above
         __syncthreads();
         if (tid == 0) {
             const unsigned int done = atomicAdd(po.local_count, 1u) + 1u;
@@ -632,11 +638,24 @@ gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bflo
                 atomicExch(po.local_count, 0u);
                 __threadfence_system();
                 for (int p = 0; p < po.n; ++p) atomicAdd_system(po.arrived[p], 1u);
+                const uint64_t t0 = global_ns();
+                for (int r = 0; r < po.world; ++r) {
+                    if (r == po.rank) continue;
+                    while (true) {
+                        unsigned int seen;
+                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(po.local_arrived + r) : "memory");
+                        if ((int)(seen - po.target) >= 0) break;
+                        if (global_ns() - t0 > 1000000000ull) {
+                            if (status) atomicExch(status, B200HT_ERR_TIMEOUT);
+                            r = po.world;
+                            break;
+                        }
+                    }
+                }
             }
         }
     }
 }
-
 
 // ---------------------------------------------------------------------------
 // fp32 (exact): H(X) in shared memory as fp32, one warp per row of W
@@ -907,31 +926,6 @@ extern "C" int b200ht_fused_gemv(const void *W, const void *X, void *Y, int M, i
     return launch_gemv(W, X, Y, M, N, B, in_dtype, out_dtype, scale, (cudaStream_t)stream);
 }
 
-namespace b200ht {
-
-// Waits (time-limited, about one second) until every other rank's arrival counter in this GPU's counter array has
-// reached `target`, i.e. until all rows of the current call have landed in this GPU's Y.  One lane per rank.  On
-// expiry the status word gets B200HT_ERR_TIMEOUT and the kernel returns: nothing hangs when a peer never arrives.
-__global__ void gemv_peer_wait_kernel(const unsigned int *arrived, unsigned int target, int world, int rank, int *status)
-{
-    pdl_launch_dependents();
-    pdl_wait();   // the local GEMV of this call is complete
-    const int s = threadIdx.x;
-    if (s >= world || s == rank) return;
-    const uint64_t t0 = global_ns();
-    while (true) {
-        unsigned int seen;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(arrived + s) : "memory");
-        if ((int)(seen - target) >= 0) return;
-        if (global_ns() - t0 > 1000000000ull) {
-            if (status) atomicExch(status, B200HT_ERR_TIMEOUT);
-            return;
-        }
-    }
-}
-
-}  // namespace b200ht
-
 extern "C" int b200ht_fused_gemv_peers(const void *W, const void *X, void *Y, int M, int N, int B, int in_dtype, int out_dtype,
                                        float scale, int n_peers, void *const *peer_y, unsigned int *const *peer_arrived,
                                        unsigned int *local_count, const unsigned int *local_arrived, int world, int rank,
@@ -956,10 +950,11 @@ extern "C" int b200ht_fused_gemv_peers(const void *W, const void *X, void *Y, in
         po.arrived[p] = peer_arrived[p];
     }
     po.local_count = local_count;
-    cudaStream_t st = (cudaStream_t)stream;
-    rc = launch_stream(W, X, Y, M, N, ilog2((uint32_t)N), B, 0, B, out_dtype, scale, st, po);
-    if (rc) return rc;
-    return launch_pdl(gemv_peer_wait_kernel, dim3(1), dim3(32), 0, st, local_arrived, target, world, rank, status_word_ptr());
+    po.local_arrived = local_arrived;
+    po.target = target;
+    po.world = world;
+    po.rank = rank;
+    return launch_stream(W, X, Y, M, N, ilog2((uint32_t)N), B, 0, B, out_dtype, scale, (cudaStream_t)stream, po);
 }
 
 // Inter-process mapping of device buffers (one process per GPU): export a handle for a buffer inside a cudaMalloc

@@ -203,7 +203,7 @@ int b200ht_fused_gemv_max_batch(int N, int in_dtype);
  *   local_count   a zero-initialised 32-bit word in this GPU's memory (scratch of the kernel, left at zero)
  *   local_arrived this GPU's array of `world` arrival counters (zero-initialised once; entry `rank` is unused)
  *   target        number of calls made so far on this exchange, this one included: all ranks call in lockstep
- * After the GEMV kernel a one-warp kernel waits, for at most one second, until every other rank's counter has reached
+ * The last CTA of the kernel to finish waits, for at most one second, until every other rank's counter has reached
  * `target`; work enqueued behind the call sees the complete Y.  If a peer never arrives the wait gives up, the status
  * word (b200ht_device_status) reports B200HT_ERR_TIMEOUT and nothing hangs.  A rank must not start call k + 2 before
  * its consumers of call k's result are enqueued: alternate between two result buffers (the Python wrapper does).
