@@ -3,6 +3,7 @@
 
     python baseline/compare.py build --ref <checkout of Alan-Chen99/6s894_project_2025>
     python baseline/compare.py run [--json out.json] [--only fwht,gemv,gemm]
+    python baseline/compare.py report --json out.json        # markdown tables of a run
 
 ``build`` compiles, from the sources where they lie in the checkout and into ``baseline/_ref/`` (git-ignored):
 
@@ -259,6 +260,55 @@ def run(args) -> None:
     print(text)
 
 
+def report(args) -> None:
+    """Markdown tables from the JSON that ``run`` wrote (what profiles/reference_kernels_on_b200.md holds)."""
+    d = json.loads(Path(args.json).read_text())
+    res = d["results"]
+    print(f"Device: {d['device']}; PyTorch {d['pytorch']}.\n")
+    for shape, title in (("rot", "(16384, n) bf16, in place on >= 512 MB of rotating buffers"),
+                         ("2p30", "2^30 elements per n, bf16, in place (the reference's own benchmark shape)")):
+        rows = [r for r in res if r.get("shape") == shape]
+        if not rows:
+            continue
+        cases = ["Ours(reference csrc)", "HadaCore", "b200ht"]
+        print(f"### Transform, {title}\n")
+        print("| n | reference `csrc` GB/s (us) | `HadaCore` GB/s (us) | this library GB/s (us) | vs `csrc` | vs `HadaCore` |")
+        print("|---:|---:|---:|---:|---:|---:|")
+        for n in sorted({r["m"] for r in rows}):
+            cell, val = {}, {}
+            for c in cases:
+                m = [r for r in rows if r["case"] == c and r["m"] == n]
+                if m:
+                    cell[c] = f"{m[0]['gbs']:.0f} ({m[0]['per_iter_ms'] * 1e3:.1f})"
+                    val[c] = m[0]["gbs"]
+                else:
+                    cell[c] = "-"
+            ratio = lambda c: f"{val['b200ht'] / val[c]:.2f}" if c in val and "b200ht" in val else "-"   # noqa: E731
+            print(f"| {n} | {cell[cases[0]]} | {cell[cases[1]]} | {cell[cases[2]]} | {ratio(cases[0])} | {ratio(cases[1])} |")
+        print()
+    rows = [r for r in res if r.get("shape") == "gemv"]
+    if rows:
+        print("### Fused GEMV, W 4096 x 4096, 16 rotating copies of W (us per call)\n")
+        print("| case | dtype | B = 1 | B = 4 | B = 16 |")
+        print("|---|---|---:|---:|---:|")
+        for case, dt in sorted({(r["case"], r["dtype"]) for r in rows}):
+            t = {r["batch"]: r["per_iter_ms"] * 1e3 for r in rows if r["case"] == case and r["dtype"] == dt}
+            print(f"| `{case}` | {dt} | " + " | ".join(f"{t[b]:.1f}" if b in t else "-" for b in (1, 4, 16)) + " |")
+        print()
+    rows = [r for r in res if r.get("shape") == "gemm_k1024_4096x4096"]
+    if rows:
+        print("### Fused W.H(X), K = 1024, 4096 tokens, M = 4096, unscaled, minimum of 8 runs\n")
+        print("| case | dtype | ms | TFLOP/s |")
+        print("|---|---|---:|---:|")
+        for r in rows:
+            print(f"| `{r['case']}` | {r['dtype']} | {r['per_iter_ms']:.3f} | {r['tflops']:.1f} |")
+        print()
+    if d.get("checks"):
+        print("Reference transform outputs against a host butterfly (4 rows per n, inputs in [-2, 2]): max |err| "
+              + ", ".join(sorted({c.split("max_abs_err=")[1] for c in d["checks"]})[:1]) + " ... "
+              + max(c.split("max_abs_err=")[1] for c in d["checks"]) + " (their own tolerance is 5e-2).")
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -267,9 +317,13 @@ def main() -> None:
     r = sub.add_parser("run")
     r.add_argument("--json", default=None)
     r.add_argument("--only", default=None, help="comma-separated subset of fwht,gemv,gemm")
+    rp = sub.add_parser("report")
+    rp.add_argument("--json", required=True)
     args = ap.parse_args()
     if args.cmd == "build":
         build(args.ref)
+    elif args.cmd == "report":
+        report(args)
     else:
         run(args)
 
