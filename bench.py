@@ -773,6 +773,61 @@ def run_profile_case(case: str):
     torch.cuda.synchronize()
 
 
+_ORDERS_CHILD = r"""
+import importlib, json, math, sys, torch
+sys.path.insert(0, %r)
+pkg = importlib.import_module("6s894_project_2025_b200")
+lib = pkg._lib.load()
+st = torch.cuda.current_stream().cuda_stream
+g = torch.Generator(device="cuda").manual_seed(4)
+def run(K, M, N, reps, layout, odt, ocode):
+    W = (torch.randn(M, K, generator=g, device="cuda") / math.sqrt(K)).bfloat16()
+    X = torch.randn(N, K, generator=g, device="cuda").bfloat16()
+    C = torch.empty((N, M) if layout == 1 else (M, N), dtype=odt, device="cuda")
+    ws = torch.empty(pkg.fused_gemm_workspace_bytes(M, N, K, torch.bfloat16), dtype=torch.uint8, device="cuda")
+    def call():
+        rc = lib.b200ht_fused_gemm(X.data_ptr(), W.data_ptr(), C.data_ptr(), M, N, K, 1, ocode, layout, float(K ** -0.5),
+                                   ws.data_ptr(), ws.numel(), st)
+        assert rc == 0
+    for _ in range(3):
+        call()
+    torch.cuda.synchronize()
+    tot = 0.0
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); call(); e1.record(); torch.cuda.synchronize()
+        tot += e0.elapsed_time(e1)
+    return tot / reps
+print(json.dumps({"c5_ms": run(8192, 28672, 16384, 8, 1, torch.bfloat16, 1),
+                  "c5_shard_2048_tokens_ms": run(8192, 28672, 2048, 10, 1, torch.bfloat16, 1),
+                  "k4096_ms": run(4096, 16384, 16384, 8, 1, torch.bfloat16, 1),
+                  "c3_ms": run(1024, 4096, 4096, 20, 0, torch.float32, 2)}))
+"""
+
+
+def run_compare_orders():
+    """``--compare orders``: the fused GEMM's tile order and chunking knobs (read once per process, hence one child
+    process per setting, two rounds), mean ms of single calls on four shapes.  One JSON line."""
+    settings = {
+        "default (token groups of 8, 32 MB chunks)": {},
+        "row groups of 16, one chunk": {"B200HT_GEMM_ORDER": "0", "B200HT_GEMM_GROUP": "16", "B200HT_GEMM_CHUNK_MB": "0"},
+        "row groups of 8, one chunk": {"B200HT_GEMM_ORDER": "0", "B200HT_GEMM_GROUP": "8", "B200HT_GEMM_CHUNK_MB": "0"},
+        "token groups of 8, one chunk": {"B200HT_GEMM_CHUNK_MB": "0"},
+        "token groups of 12, 48 MB chunks": {"B200HT_GEMM_GROUP": "12", "B200HT_GEMM_CHUNK_MB": "48"},
+        "128-row tiles only": {"B200HT_GEMM_MT": "1"},
+    }
+    out = {k: [] for k in settings}
+    for _ in range(2):
+        for name, env in settings.items():
+            r = subprocess.run([sys.executable, "-c", _ORDERS_CHILD % str(ROOT)], capture_output=True, text=True,
+                               env=dict(os.environ, **env))
+            try:
+                out[name].append(json.loads(r.stdout.strip().splitlines()[-1]))
+            except (IndexError, ValueError):
+                out[name].append({"error": (r.stdout + r.stderr)[-300:]})
+    print(json.dumps({"compare": "orders", "ms_per_call": out}))
+
+
 def run_compare(which: str):
     """Same-box library comparators (``--compare cublas``), one JSON line.  Nothing here is on the product path: the
     library kernels are timed beside this repository's calls on the same buffers.
@@ -784,6 +839,8 @@ def run_compare(which: str):
     import torch
     import torch.nn.functional as F
 
+    if which == "orders":
+        return run_compare_orders()
     assert which == "cublas"
     pkg = importlib.import_module("6s894_project_2025_b200")
     torch.cuda.set_device(0)
@@ -860,7 +917,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--profile-case", default=None, choices=["gemm", "gemm-full", "fwht", "fwht-sweep", "gemv", "c3"],
                     help="run a few launches of ONE kernel on a reduced shape and exit (for ncu captures)")
-    ap.add_argument("--compare", default=None, choices=["cublas"],
+    ap.add_argument("--compare", default=None, choices=["cublas", "orders"],
                     help="time library comparators beside this repository's calls on one GPU and exit")
     args = ap.parse_args()
     if args.profile_case:
