@@ -625,14 +625,14 @@ gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bflo
         __syncthreads();
     }
     if (po.n) {
-        // Publish: the threads that stored make their peer stores visible system-wide; the last CTA of the launch to
+        // Publish: one thread per CTA makes the CTA's peer stores visible system-wide; the last CTA of the launch to
         // get here bumps this rank's counter on every peer (a peer that sees the count sees all rows of this launch)
         // and then waits, for at most a second, until the other ranks' counters on THIS GPU have reached the call's
         // target: when the kernel is complete, so is Y.  If a peer never arrives the wait gives up with
         // B200HT_ERR_TIMEOUT in the status word; nothing hangs.
-        if (tid < 32 * Bg && ngroups > 0) __threadfence_system();   // the threads of the store loops above
         __syncthreads();
         if (tid == 0) {
+            __threadfence_system();   // cumulative: covers the peer stores of the whole CTA, ordered before it by the barrier
             const unsigned int done = atomicAdd(po.local_count, 1u) + 1u;
             if (done == gridDim.x) {
                 atomicExch(po.local_count, 0u);
