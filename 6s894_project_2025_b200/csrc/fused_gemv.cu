@@ -859,7 +859,7 @@ int launch_gemv(const void *W, const void *X, void *Y, int M, int N, int B, int 
         return 0;
     }
     // bf16, 256 <= N <= 8192.  Two kernels cover these shapes: the mma.sync streaming kernel below (the default: it is
-    // the faster one on a B200, 8.5-9 us against 9.8-10 us at W 4096 x 4096, B <= 4) and the tcgen05 kernel of
+    // the faster one on a B200, 8.5-9 us against 9.5-9.8 us at W 4096 x 4096, B <= 4) and the tcgen05 kernel of
     // fused_gemv_tc.cu, selected with B200HT_GEMV_TCGEN05=1 (read once per process).
     static const bool use_tcgen05 = [] {
         const char *e = std::getenv("B200HT_GEMV_TCGEN05");

@@ -394,7 +394,9 @@ gemv_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmMain, const __grid_con
     if (warp == 0) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc_bf16(128, r8 * cpn);
+            // NU = 8: the eight chunk blocks that matter are 64 operand rows, and an M = 64 instruction costs its
+            // issuer 52 ns against 84 ns for M = 128
+            const uint32_t idesc = umma_idesc_bf16(NU == 8 ? 64 : 128, r8 * cpn);
             const int steps = kc / cpn;   // instruction groups (cpn chunks each) per ring item
             bool ok = true;
             for (int g = 0; g < ngroups && ok; ++g) {
@@ -452,9 +454,12 @@ gemv_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmMain, const __grid_con
         // Accumulator lane L = 32 * q + lane holds column b = L % NU of H(X) for chunk block j' = L / NU; its wanted
         // values are the 32 accumulator columns of the same chunk block (the rows of the group), if j' < cpn.
         const int q = warp & 3;
-        const int L = q * 32 + lane;
-        const int jmine = L / NU;
-        constexpr int JPW = NU >= 32 ? 1 : 32 / NU;   // chunk blocks per warp
+        // (an M = 64 accumulator, NU = 8, keeps 16 operand rows per lane quadrant, in lanes 0..15)
+        constexpr int RPQ = NU == 8 ? 16 : 32;        // accumulator rows per lane quadrant
+        const bool has_row = lane < RPQ;
+        const int L = q * RPQ + (has_row ? lane : 0);
+        const int jmine = has_row ? L / NU : -1;
+        constexpr int JPW = NU >= RPQ ? 1 : RPQ / NU;  // chunk blocks per warp
         const int et = tid - 4 * 32;                  // 0..127 within the epilogue warps
         // Warp 4 waits for the accumulator and publishes the outcome; the named barrier that follows is executed by
         // all four warps whatever the outcome, so they leave the loop together if the wait gave up.  The same
@@ -471,7 +476,7 @@ gemv_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmMain, const __grid_con
             uint32_t keep[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) keep[j] = 0u;
-            const int jfirst = (q * 32) / NU;
+            const int jfirst = (q * RPQ) / NU;
 #pragma unroll
             for (int sub = 0; sub < JPW; ++sub) {
                 const int jb = jfirst + sub;          // warp-uniform
@@ -489,10 +494,12 @@ gemv_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmMain, const __grid_con
             __syncwarp();
             if (lane == 0) mbar_arrive(acce_bar(slot));
             // add the chunk blocks through shared memory and store
+            if (has_row) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 4)
-                *(float4 *)(red + L * 32 + j) = make_float4(__uint_as_float(keep[j]), __uint_as_float(keep[j + 1]),
-                                                            __uint_as_float(keep[j + 2]), __uint_as_float(keep[j + 3]));
+                for (int j = 0; j < 32; j += 4)
+                    *(float4 *)(red + L * 32 + j) = make_float4(__uint_as_float(keep[j]), __uint_as_float(keep[j + 1]),
+                                                                __uint_as_float(keep[j + 2]), __uint_as_float(keep[j + 3]));
+            }
             asm volatile("bar.sync 1, 128;\n" ::: "memory");
             const long row0 = (long)(g_begin + g) * group_rows;
             for (int idx = et; idx < group_rows * Bg; idx += 128) {
