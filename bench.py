@@ -636,7 +636,12 @@ def run_gpu_arm(args):
     gemv = time_gemv(pkg, torch, peaks)
     c3 = time_c3(pkg, torch, peaks)
     k4096 = time_k4096(pkg, torch, peaks)
-    gemv_rows = time_gemv_rows(pkg, torch, dist, rank, world) if world > 1 else None
+    gemv_rows = None
+    if world > 1:
+        try:
+            gemv_rows = time_gemv_rows(pkg, torch, dist, rank, world)
+        except Exception as e:   # noqa: BLE001 -- a secondary block must not take the headline line down with it
+            gemv_rows = {"error": f"{type(e).__name__}: {e}"[:300]}
     if world > 1:
         agg = torch.tensor([fwht[k]["gbs"] for k in sorted(fwht, key=int)], device="cuda")
         dist.all_reduce(agg, op=dist.ReduceOp.SUM)
