@@ -38,6 +38,7 @@ constexpr int GT_WARPS = 16;
 constexpr int GT_THREADS = GT_WARPS * 32;
 constexpr int GT_TILE_ROWS = 32;         // rows of a ring tile (a row group has at most that many rows of W)
 constexpr int GT_MAX_STAGES = 16;        // the first fill is issued by one lane per stage
+constexpr int GT_RED_PITCH = 33;         // floats per accumulator row of the reduction buffer (odd: no bank conflicts)
 
 // Byte offset of the 16-byte vector v (elements 8v .. 8v+7) of column `col` in the B operand: 64-k chunks of NU
 // rows x 128 bytes, 16-byte pieces XOR-swizzled by the row's low three bits.
@@ -181,8 +182,8 @@ gemv_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmMain, const __grid_con
     unsigned char *gen = smem_dyn + (ring_s - smem_u32(smem_dyn));
     unsigned char *hx = gen + (size_t)nstages * stage_bytes;                      // [N/64][NU][128 bytes]
     const uint32_t hx_s = ring_s + (uint32_t)(nstages * stage_bytes);
-    float *red = (float *)(hx + (size_t)N * NU * 2);                                // [128 accumulator rows][32]
-    unsigned char *bar_mem = (unsigned char *)(red + 128 * GT_TILE_ROWS);
+    float *red = (float *)(hx + (size_t)N * NU * 2);                      // [128 accumulator rows][GT_RED_PITCH]
+    unsigned char *bar_mem = (unsigned char *)(red + 128 * GT_RED_PITCH);
     const uint32_t bar_s = smem_u32(bar_mem);
     auto full_bar = [&](int s) { return bar_s + 8u * s; };                        // TMA landed
     auto empty_bar = [&](int s) { return bar_s + 8u * (GT_MAX_STAGES + s); };     // the MMAs reading the stage are done
@@ -494,18 +495,19 @@ gemv_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmMain, const __grid_con
             __syncwarp();
             if (lane == 0) mbar_arrive(acce_bar(slot));
             // add the chunk blocks through shared memory and store
+            // (rows of GT_RED_PITCH floats: the lanes of a warp write, and later read, different banks.  With rows of
+            // 128 bytes the 16-byte stores of a warp all fell on the same four banks, and the loads queued behind
+            // them: 0.5 us per row group at one column, 2.5 us at sixteen.)
             if (has_row) {
 #pragma unroll
-                for (int j = 0; j < 32; j += 4)
-                    *(float4 *)(red + L * 32 + j) = make_float4(__uint_as_float(keep[j]), __uint_as_float(keep[j + 1]),
-                                                                __uint_as_float(keep[j + 2]), __uint_as_float(keep[j + 3]));
+                for (int j = 0; j < 32; ++j) red[L * GT_RED_PITCH + j] = __uint_as_float(keep[j]);
             }
             asm volatile("bar.sync 1, 128;\n" ::: "memory");
             const long row0 = (long)(g_begin + g) * group_rows;
             for (int idx = et; idx < group_rows * Bg; idx += 128) {
                 const int rg = idx / Bg, c = idx - rg * Bg;
                 float sum = 0.f;
-                for (int j = 0; j < cpn; ++j) sum += red[(j * NU + c) * 32 + rg];
+                for (int j = 0; j < cpn; ++j) sum += red[(j * NU + c) * GT_RED_PITCH + rg];
                 const long row = row0 + rg;
                 if (row < M) {
                     const size_t o = (size_t)row * B + b0 + c;
@@ -531,7 +533,7 @@ constexpr size_t kTcSmemLimit = 225 * 1024;
 constexpr size_t kTcMinRing = 48 * 1024;
 static size_t tc_fixed_smem(int N, int nu)
 {
-    return (size_t)N * nu * 2 + (size_t)128 * GT_TILE_ROWS * 4 /*reduction*/ + 1024 /*alignment*/ + 8 * (2 * GT_MAX_STAGES + 4) + 64;
+    return (size_t)N * nu * 2 + (size_t)128 * GT_RED_PITCH * 4 /*reduction*/ + 1024 /*alignment*/ + 8 * (2 * GT_MAX_STAGES + 4) + 64;
 }
 static int nu_of(int cols) { return cols <= 8 ? 8 : (cols <= 16 ? 16 : (cols <= 32 ? 32 : 64)); }
 
