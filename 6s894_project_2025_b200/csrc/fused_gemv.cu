@@ -629,29 +629,37 @@ gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bflo
         // get here bumps this rank's counter on every peer (a peer that sees the count sees all rows of this launch)
         // and then waits, for at most a second, until the other ranks' counters on THIS GPU have reached the call's
         // target: when the kernel is complete, so is Y.  If a peer never arrives the wait gives up with
-        // B200HT_ERR_TIMEOUT in the status word; nothing hangs.
+        // B200HT_ERR_TIMEOUT in the status word; nothing hangs.  Signals and waits take one lane per peer, so their
+        // latency over the links is paid once, not once per peer.
         __syncthreads();
-        if (tid == 0) {
-            __threadfence_system();   // cumulative: covers the peer stores of the whole CTA, ordered before it by the barrier
-            const unsigned int done = atomicAdd(po.local_count, 1u) + 1u;
+        if (warp == 0) {
+            unsigned int done = 0;
+            if (lane == 0) {
+                __threadfence_system();   // cumulative: covers the peer stores of the whole CTA, ordered before it by the barrier
+                done = atomicAdd(po.local_count, 1u) + 1u;
+            }
+            done = __shfl_sync(0xffffffffu, done, 0);
             if (done == gridDim.x) {
-                atomicExch(po.local_count, 0u);
-                __threadfence_system();
-                for (int p = 0; p < po.n; ++p) atomicAdd_system(po.arrived[p], 1u);
-                const uint64_t t0 = global_ns();
-                for (int r = 0; r < po.world; ++r) {
-                    if (r == po.rank) continue;
+                if (lane == 0) {
+                    atomicExch(po.local_count, 0u);
+                    __threadfence_system();
+                }
+                __syncwarp();
+                if (lane < po.n)
+                    asm volatile("red.release.sys.global.add.u32 [%0], 1;\n" ::"l"(po.arrived[lane]) : "memory");
+                if (lane < po.world && lane != po.rank) {
+                    const uint64_t t0 = global_ns();
                     while (true) {
                         unsigned int seen;
-                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(po.local_arrived + r) : "memory");
+                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(po.local_arrived + lane) : "memory");
                         if ((int)(seen - po.target) >= 0) break;
                         if (global_ns() - t0 > 1000000000ull) {
                             if (status) atomicExch(status, B200HT_ERR_TIMEOUT);
-                            r = po.world;
                             break;
                         }
                     }
                 }
+                __syncwarp();
             }
         }
     }

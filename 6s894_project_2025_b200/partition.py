@@ -195,6 +195,7 @@ class _IpcBackend:
     def __init__(self, device):
         from . import _lib
         self.device = device
+        self.index = device.index if device.index is not None else torch.cuda.current_device()
         self._lib = _lib
         self.lib = _lib.load()
         self._opened = {}
@@ -247,12 +248,21 @@ class _IpcBackend:
             self._args[key] = args
         peer_y, peer_arrived, n, in_dt, out_dt, default_scale = args
         sc = default_scale if scale is None else scale
-        with torch.cuda.device(self.device):
-            rc = self.lib.b200ht_fused_gemv_peers(
+
+        def enqueue():
+            return self.lib.b200ht_fused_gemv_peers(
                 op.W.data_ptr(), X.data_ptr(), p["y_local"], op.row_end - op.row_begin, op.N, batch, in_dt, out_dt,
                 float(sc), n, peer_y, peer_arrived, p["local_count"], p["local_arrived"], op.world, op.rank,
-                p["target"], int(torch.cuda.current_stream(self.device).cuda_stream))
-        self._lib.check(rc, "b200ht_fused_gemv_peers")
+                p["target"], torch.cuda.current_stream(self.device).cuda_stream)
+
+        # (switching the device costs more host time than the call; one process per GPU is already on it)
+        if torch.cuda.current_device() == self.index:
+            rc = enqueue()
+        else:
+            with torch.cuda.device(self.device):
+                rc = enqueue()
+        if rc:
+            self._lib.check(rc, "b200ht_fused_gemv_peers")
 
     def view(self, buf: torch.Tensor, offset: int, shape, dtype) -> torch.Tensor:
         n = shape[0] * shape[1] * (4 if dtype == torch.float32 else 2)

@@ -318,22 +318,25 @@ def time_gemv_rows(pkg, torch, dist, rank, world, reps=20):
             torch.cuda.synchronize()
             dist.barrier()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            h0 = time.perf_counter()
             e0.record()
             for _ in range(reps):
                 for i in range(len(Ws)):
                     call(i)
             e1.record()
+            h1 = time.perf_counter()       # the host has enqueued everything; the device may still be running
             torch.cuda.synchronize()
-            t = torch.tensor([e0.elapsed_time(e1) / (reps * len(Ws))], device="cuda")
+            t = torch.tensor([e0.elapsed_time(e1) / (reps * len(Ws)), (h1 - h0) * 1e3 / (reps * len(Ws))], device="cuda")
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            return float(t.item())
+            return float(t[0].item()), float(t[1].item())
 
-        ms = timed(lambda i: ops[i](X))
-        nccl_ms = timed(lambda i: pkg.gather_rows(pkg.fused_ht_gemv(Ws[i], X), M))
+        ms, host_ms = timed(lambda i: ops[i](X))
+        nccl_ms, _ = timed(lambda i: pkg.gather_rows(pkg.fused_ht_gemv(Ws[i], X), M))
         status = pkg.device_status()
         out[f"{M}x{N}"] = {"ms": ms, "gbs_all_gpus": M * N * 2 / (ms * 1e-3) / 1e9, "rows_per_gpu": b - a,
                            "parity": bool(parity.item()) and status == 0, "rel_err_vs_one_gpu": err,
-                           "nccl_all_gather_ms": nccl_ms, "exchange": "peer stores + arrival counters"}
+                           "nccl_all_gather_ms": nccl_ms, "host_enqueue_ms": host_ms,
+                           "exchange": "peer stores + arrival counters"}
         for op in ops:
             op.close()
         del Ws, ops
