@@ -281,9 +281,10 @@ struct PeerOut {
     int n;
     unsigned char *y[7];        // the peers' Y buffers, offset to this rank's first row
     unsigned int *arrived[7];   // this rank's arrival counter on each peer
-    unsigned int *local_count;  // CTAs of this launch that have finished (self-resetting)
+    unsigned int *local_count;  // 8-byte aligned pair: CTAs of this launch that have finished (self-resetting), calls made
     const unsigned int *local_arrived;   // this GPU's array of arrival counters, one per rank
-    unsigned int target;        // value the other ranks' counters reach when their rows of this call have landed
+    unsigned int target;        // value the other ranks' counters reach when their rows of this call have landed;
+                                // 0: the number of this call as counted in local_count[1]
     int world, rank;
 };
 
@@ -633,26 +634,41 @@ gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bflo
         // latency over the links is paid once, not once per peer.
         __syncthreads();
         if (warp == 0) {
-            unsigned int done = 0;
+            // local_count is one 64-bit word: finished CTAs of this launch in the low half, calls made in the high
+            // half.  One returning atomic per CTA is the only round trip here; the last CTA learns the number of the
+            // call from it and, with one more (non-returning) atomic, clears the low half and counts the call.
+            unsigned long long old = 0;
             if (lane == 0) {
-                __threadfence_system();   // cumulative: covers the peer stores of the whole CTA, ordered before it by the barrier
-                done = atomicAdd(po.local_count, 1u) + 1u;
+                // cumulative: covers the peer stores of the whole CTA, ordered before it by the barrier (an
+                // acquire-release fence: the sequentially consistent one of __threadfence_system is not needed)
+                asm volatile("fence.acq_rel.sys;\n" ::: "memory");
+                old = atomicAdd((unsigned long long *)po.local_count, 1ull);
             }
-            done = __shfl_sync(0xffffffffu, done, 0);
-            if (done == gridDim.x) {
+            old = __shfl_sync(0xffffffffu, old, 0);
+            if ((unsigned int)old + 1u == gridDim.x) {
+                const unsigned int target = po.target ? po.target : (unsigned int)(old >> 32) + 1u;
                 if (lane == 0) {
-                    atomicExch(po.local_count, 0u);
-                    __threadfence_system();
+                    asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;\n" ::"l"(po.local_count),
+                                 "l"((1ull << 32) - (unsigned long long)gridDim.x)
+                                 : "memory");
+                    asm volatile("fence.acq_rel.sys;\n" ::: "memory");   // the other CTAs' fences, seen through the counter, before the signals
                 }
-                __syncwarp();
+                __syncwarp();   // lane 0's fence before the other lanes' signals
+                // (lane 0's fence above, ordered before these by the warp barrier, is the release: the signals
+                // themselves are relaxed, and so are the polls up to the last one)
                 if (lane < po.n)
-                    asm volatile("red.release.sys.global.add.u32 [%0], 1;\n" ::"l"(po.arrived[lane]) : "memory");
+                    asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;\n" ::"l"(po.arrived[lane]) : "memory");
                 if (lane < po.world && lane != po.rank) {
                     const uint64_t t0 = global_ns();
                     while (true) {
                         unsigned int seen;
-                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(po.local_arrived + lane) : "memory");
-                        if ((int)(seen - po.target) >= 0) break;
+                        asm volatile("ld.relaxed.sys.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(po.local_arrived + lane) : "memory");
+                        if ((int)(seen - target) >= 0) {
+                            // seen it: read it once more as an acquire, which orders the peer's rows before
+                            // whatever follows this kernel
+                            asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(po.local_arrived + lane) : "memory");
+                            break;
+                        }
                         if (global_ns() - t0 > 1000000000ull) {
                             if (status) atomicExch(status, B200HT_ERR_TIMEOUT);
                             break;
@@ -947,7 +963,8 @@ extern "C" int b200ht_fused_gemv_peers(const void *W, const void *X, void *Y, in
     if (n_peers < 0 || n_peers > 7 || world < 1 || world > 8 || rank < 0 || rank >= world) return B200HT_ERR_SIZE;
     if (!W || !X || !Y || !local_count || !local_arrived || (n_peers && (!peer_y || !peer_arrived))) return B200HT_ERR_NULL;
     // Y points into the middle of a result buffer (this rank's first row): element alignment is all it needs
-    if (!aligned16(W) || !aligned16(X) || ((uintptr_t)Y & (out_dtype == B200HT_F32 ? 3u : 1u))) return B200HT_ERR_ALIGN;
+    if (!aligned16(W) || !aligned16(X) || ((uintptr_t)Y & (out_dtype == B200HT_F32 ? 3u : 1u)) || ((uintptr_t)local_count & 7u))
+        return B200HT_ERR_ALIGN;
     int rc = check_device();
     if (rc) return rc;
     PeerOut po{};

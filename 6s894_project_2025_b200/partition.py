@@ -105,6 +105,11 @@ class RowShardedGemv:
     -- exports it (CUDA IPC), the handles go round with ``all_gather_object`` and every rank maps the others'.
     ``__call__`` returns a view of the result buffer of this call; it stays valid until the call after next.  All
     ranks must make the same sequence of calls.  bf16, 256 <= N <= 8192, B <= ``max_batch``.
+
+    The kernel counts the calls of an exchange on the device, so no argument changes from one call to the next and
+    a CUDA graph can replay calls (which takes the host's launch pace and jitter, the larger part of a call's time
+    on 4 and 8 GPUs, out of the loop).  A captured graph must hold an even number of calls of each op: the two
+    result buffers alternate.
     """
 
     def __init__(self, W_local: torch.Tensor, n_rows: int, max_batch: int, *, out_dtype: torch.dtype = torch.float32,
@@ -142,12 +147,12 @@ class RowShardedGemv:
     def _arrived(self, base: int, src_rank: int) -> int:
         return base + 4 * src_rank             # arrival counter of rank src_rank
     def _local_count(self, base: int) -> int:
-        return base + 128                      # kernel scratch word
+        return base + 128                      # kernel scratch word, then the kernel's count of calls
     def _rows(self, base: int, parity: int, row: int, batch: int, esz: int) -> int:
         return base + 256 + parity * self.y_bytes + row * batch * esz
 
     def plan(self, batch: int) -> dict:
-        """Addresses and counter target of the NEXT call (also what the host-side tests check)."""
+        """Addresses and number of the NEXT call (also what the host-side tests check)."""
         if not (1 <= batch <= self.max_batch):
             raise RuntimeError(f"RowShardedGemv: batch must be in [1, {self.max_batch}]")
         parity = self.calls & 1
@@ -165,7 +170,7 @@ class RowShardedGemv:
                 "y_full": self._rows(mine, parity, 0, batch, esz),
             }
             self._plans[(batch, parity)] = p
-        p["target"] = self.calls + 1
+        p["call"] = self.calls + 1      # the value the arrival counters reach with this call (the kernel keeps its own count)
         return p
 
     def __call__(self, X: torch.Tensor, *, scale: float | None = None) -> torch.Tensor:
@@ -253,7 +258,7 @@ class _IpcBackend:
             return self.lib.b200ht_fused_gemv_peers(
                 op.W.data_ptr(), X.data_ptr(), p["y_local"], op.row_end - op.row_begin, op.N, batch, in_dt, out_dt,
                 float(sc), n, peer_y, peer_arrived, p["local_count"], p["local_arrived"], op.world, op.rank,
-                p["target"], torch.cuda.current_stream(self.device).cuda_stream)
+                0, torch.cuda.current_stream(self.device).cuda_stream)   # 0: calls counted on the device
 
         # (switching the device costs more host time than the call; one process per GPU is already on it)
         if torch.cuda.current_device() == self.index:

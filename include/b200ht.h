@@ -200,9 +200,12 @@ int b200ht_fused_gemv_max_batch(int N, int in_dtype);
  *   peer_y[p]     the same position inside peer p's full result buffer (n_peers <= 7 pointers valid on this GPU,
  *                 e.g. from b200ht_ipc_open)
  *   peer_arrived[p]  address, in peer p's memory, of the 32-bit arrival counter that belongs to THIS rank
- *   local_count   a zero-initialised 32-bit word in this GPU's memory (scratch of the kernel, left at zero)
+ *   local_count   two zero-initialised 32-bit words in this GPU's memory, 8-byte aligned (the kernel updates them
+ *                 as one 64-bit word): [0] scratch, left at zero; [1] calls made so far, counted by the kernel
  *   local_arrived this GPU's array of `world` arrival counters (zero-initialised once; entry `rank` is unused)
- *   target        number of calls made so far on this exchange, this one included: all ranks call in lockstep
+ *   target        number of calls made so far on this exchange, this one included: all ranks call in lockstep.
+ *                 0 = take it from local_count[1]: no argument then changes from call to call, so a CUDA graph can
+ *                 replay the call (use one way of counting per exchange, not both)
  * The last CTA of the kernel to finish waits, for at most one second, until every other rank's counter has reached
  * `target`; work enqueued behind the call sees the complete Y.  If a peer never arrives the wait gives up, the status
  * word (b200ht_device_status) reports B200HT_ERR_TIMEOUT and nothing hangs.  A rank must not start call k + 2 before

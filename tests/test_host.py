@@ -209,7 +209,7 @@ def test_two_rank_gloo_peer_store_gemv_bookkeeping(tmp_path):
             y = op(torch.zeros(N, B, dtype=torch.bfloat16))
             plan = Fake.launches[-1]
             assert y.shape == (M, B)
-            assert plan["target"] == call + 1 and plan["parity"] == call % 2
+            assert plan["call"] == call + 1 and plan["parity"] == call % 2
             mine, peer = 1000000 * (rank + 1), 1000000 * (other + 1)
             row_off = 256 + (call % 2) * op.y_bytes + a * B * 4
             assert plan["y_local"] == mine + row_off and plan["peer_y"] == [peer + row_off]

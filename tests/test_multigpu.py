@@ -108,6 +108,26 @@ def test_two_gpu_row_sharded_gemv_with_peer_stores(tmp_path):
                 full = pkg.fused_ht_gemv(W, X, out_dtype=odt)
                 err = float((got.float() - full.float()).norm() / full.float().norm())
                 assert err < (1e-5 if odt == torch.float32 else 1e-2), f"peer-store result differs: {{err}}"
+            # the same calls replayed from a CUDA graph (the kernel counts the calls itself): two calls per graph,
+            # so the result buffers keep alternating; new X before every replay
+            X = torch.randn(N, 4, generator=g).bfloat16().cuda()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    y0 = op(X)
+                    y1 = op(X)
+            for rep in range(3):
+                X.copy_(torch.randn(N, 4, generator=g).bfloat16())
+                graph.replay()
+                torch.cuda.synchronize()
+                full = pkg.fused_ht_gemv(W, X, out_dtype=odt).float()
+                for y in (y0, y1):
+                    err = float((y.float() - full).norm() / full.norm())
+                    assert err < (1e-5 if odt == torch.float32 else 1e-2), f"graph replay {{rep}} differs: {{err}}"
+            got = op(X).clone()      # and an ordinary call behind the replays
+            assert float((got.float() - full).norm() / full.norm()) < (1e-5 if odt == torch.float32 else 1e-2)
             op.close()
         assert pkg.device_status() == 0
         dist.barrier(); dist.destroy_process_group()
