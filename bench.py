@@ -46,6 +46,7 @@ import os
 import statistics
 import subprocess
 import sys
+import threading
 import time
 from pathlib import Path
 
@@ -54,6 +55,7 @@ sys.path.insert(0, str(ROOT))
 
 K_DIM, M_DIM, N_TOKENS = 8192, 28672, 16384
 CPU_SAMPLE_TOKENS = 4096  # bounded slice for the CPU legs: ~1-2 s of host work per step
+GEMV_ROWS_LIMIT_S = 150   # time limit of the row-sharded GEMV block (it normally takes a few seconds)
 METRIC = "fused W.H(X) TFLOP/s (K=8192, M=28672, 16384 tokens, bf16 in / fp32 acc); FWHT HBM GB/s in 'fwht'"
 
 
@@ -669,19 +671,15 @@ def run_gpu_arm(args):
     gemv = time_gemv(pkg, torch, peaks)
     c3 = time_c3(pkg, torch, peaks)
     k4096 = time_k4096(pkg, torch, peaks)
-    gemv_rows = None
-    if world > 1:
-        try:
-            gemv_rows = time_gemv_rows(pkg, torch, dist, rank, world)
-        except Exception as e:   # noqa: BLE001 -- a secondary block must not take the headline line down with it
-            gemv_rows = {"error": f"{type(e).__name__}: {e}"[:300]}
     if world > 1:
         agg = torch.tensor([fwht[k]["gbs"] for k in sorted(fwht, key=int)], device="cuda")
         dist.all_reduce(agg, op=dist.ReduceOp.SUM)
         for k, v in zip(sorted(fwht, key=int), agg.tolist()):
             fwht[k]["gbs_all_gpus"] = v
 
-    if rank == 0:
+    def emit(gemv_rows):
+        if rank != 0:
+            return
         cpu = None
         if world == 1:
             import torch as _t
@@ -740,7 +738,26 @@ def run_gpu_arm(args):
             "gpu_launches": gpu_launches,
             "clocks": clocks,
         }
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
+
+    # The row-sharded GEMV block runs last and under a time limit: it is the only part of the run in which ranks wait
+    # for one another outside a collective of the headline path, and a secondary block must not take the line down
+    # with it.  If it fails, or does not return in time, the line is printed without its figures.
+    gemv_rows = None
+    if world > 1:
+        def give_up():
+            emit({"error": f"no result within {GEMV_ROWS_LIMIT_S} s"})
+            os._exit(0)
+
+        timer = threading.Timer(GEMV_ROWS_LIMIT_S, give_up)
+        timer.daemon = True
+        timer.start()
+        try:
+            gemv_rows = time_gemv_rows(pkg, torch, dist, rank, world)
+        except Exception as e:   # noqa: BLE001
+            gemv_rows = {"error": f"{type(e).__name__}: {e}"[:300]}
+        timer.cancel()
+    emit(gemv_rows)
     if world > 1:
         dist.destroy_process_group()
 
