@@ -70,8 +70,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.b200ht_fused_gemv_max_batch.restype = i
     lib.b200ht_fused_gemv_max_batch.argtypes = [i, i]
     lib.b200ht_fused_gemv_peers.restype = i
-    lib.b200ht_fused_gemv_peers.argtypes = [vp, vp, vp, i, i, i, i, i, f, i, ctypes.POINTER(vp), ctypes.POINTER(vp), vp, vp,
-                                            i, i, ctypes.c_uint, vp]
+    lib.b200ht_fused_gemv_peers.argtypes = [vp, vp, vp, i, i, i, i, i, f, i, i, i, ctypes.POINTER(vp), vp, vp,
+                                            ctypes.c_uint, vp]
     lib.b200ht_ipc_export.restype = i
     lib.b200ht_ipc_export.argtypes = [vp, ctypes.c_char_p, ctypes.POINTER(ctypes.c_ulonglong)]
     lib.b200ht_ipc_open.restype = i

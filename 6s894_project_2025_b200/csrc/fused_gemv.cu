@@ -274,18 +274,17 @@ __device__ __forceinline__ uint32_t lds32(uint32_t saddr)
     return v;
 }
 
-// Row-sharded GEMV across GPUs: besides its own Y the kernel writes every result into the Y buffers of up to seven
-// peer GPUs (plain stores through peer-mapped pointers, no multicast) and, once all CTAs of the launch have done so,
-// bumps this rank's arrival counter on every peer.  n = 0: single-GPU call.
+// Row-sharded GEMV across GPUs: besides its own rows of Y the kernel sends every result, tagged with the number of the
+// call, into a slot array on each of up to seven peer GPUs (plain 8-byte stores through peer-mapped pointers, no
+// multicast), and collects the peers' rows from its own slot array into the full result.  n = 0: single-GPU call.
 struct PeerOut {
-    int n;
-    unsigned char *y[7];        // the peers' Y buffers, offset to this rank's first row
-    unsigned int *arrived[7];   // this rank's arrival counter on each peer
-    unsigned int *local_count;  // 8-byte aligned pair: CTAs of this launch that have finished (self-resetting), calls made
-    const unsigned int *local_arrived;   // this GPU's array of arrival counters, one per rank
-    unsigned int target;        // value the other ranks' counters reach when their rows of this call have landed;
-                                // 0: the number of this call as counted in local_count[1]
-    int world, rank;
+    int n;                              // peers (0: an ordinary single-GPU call)
+    unsigned long long *slots[7];       // the peers' slot arrays of this call (index: row of the full result * B + column)
+    const unsigned long long *my_slots; // this GPU's slot array, filled by the peers
+    void *y_full;                       // this GPU's full result (all ranks' rows)
+    unsigned int *local_count;          // 8-byte aligned pair: CTAs of this launch that have finished (self-resetting), calls made
+    unsigned int target;                // number of this call = tag of its slots; 0: the number counted in local_count[1]
+    int row_begin, rows_total;          // this rank's first row in the full result, rows of the full result
 };
 
 template <int NT>
@@ -341,6 +340,12 @@ gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bflo
             asm volatile("prefetch.global.L2 [%0];\n" ::"l"((const unsigned char *)X + off));
     }
     pdl_wait();
+    // row-sharded call: the number of the call tags every value sent to a peer (read now, used at the end)
+    unsigned int tag = po.target;
+    if (po.n && tag == 0u) {
+        asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];\n" : "=r"(tag) : "l"(po.local_count + 1) : "memory");
+        tag += 1u;
+    }
 
     // one TMA op per ring item: group_rows x (64*kc) elements of W (issued by one thread)
     auto issue = [&](int item) {
@@ -620,63 +625,56 @@ gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bflo
             const int row = grp_row0 + r;
             if (r < group_rows && row < row_end) {
                 store_out(Y, (size_t)row * B + b0 + c, sum, out_dtype);
-                for (int p = 0; p < po.n; ++p) store_out(po.y[p], (size_t)row * B + b0 + c, sum, out_dtype);
+                // the same value, with the call's tag beside it, into the slot arrays of the other ranks: one 8-byte
+                // store each, which arrives whole, so a peer that reads the tag has the value
+                const size_t slot = (size_t)(po.row_begin + row) * B + c;
+#pragma unroll
+                for (int p = 0; p < 7; ++p)
+                    if (p < po.n)
+                        asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};\n" ::"l"(po.slots[p] + slot),
+                                     "r"(__float_as_uint(sum)), "r"(tag)
+                                     : "memory");
             }
         }
         __syncthreads();
     }
     if (po.n) {
-        // Publish: one thread per CTA makes the CTA's peer stores visible system-wide; the last CTA of the launch to
-        // get here bumps this rank's counter on every peer (a peer that sees the count sees all rows of this launch)
-        // and then waits, for at most a second, until the other ranks' counters on THIS GPU have reached the call's
-        // target: when the kernel is complete, so is Y.  If a peer never arrives the wait gives up with
-        // B200HT_ERR_TIMEOUT in the status word; nothing hangs.  Signals and waits take one lane per peer, so their
-        // latency over the links is paid once, not once per peer.
-        __syncthreads();
-        if (warp == 0) {
-            // local_count is one 64-bit word: finished CTAs of this launch in the low half, calls made in the high
-            // half.  One returning atomic per CTA is the only round trip here; the last CTA learns the number of the
-            // call from it and, with one more (non-returning) atomic, clears the low half and counts the call.
-            unsigned long long old = 0;
-            if (lane == 0) {
-                // cumulative: covers the peer stores of the whole CTA, ordered before it by the barrier (an
-                // acquire-release fence: the sequentially consistent one of __threadfence_system is not needed)
-                asm volatile("fence.acq_rel.sys;\n" ::: "memory");
-                old = atomicAdd((unsigned long long *)po.local_count, 1ull);
-            }
-            old = __shfl_sync(0xffffffffu, old, 0);
-            if ((unsigned int)old + 1u == gridDim.x) {
-                const unsigned int target = po.target ? po.target : (unsigned int)(old >> 32) + 1u;
-                if (lane == 0) {
-                    asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;\n" ::"l"(po.local_count),
-                                 "l"((1ull << 32) - (unsigned long long)gridDim.x)
-                                 : "memory");
-                    asm volatile("fence.acq_rel.sys;\n" ::: "memory");   // the other CTAs' fences, seen through the counter, before the signals
-                }
-                __syncwarp();   // lane 0's fence before the other lanes' signals
-                // (lane 0's fence above, ordered before these by the warp barrier, is the release: the signals
-                // themselves are relaxed, and so are the polls up to the last one)
-                if (lane < po.n)
-                    asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;\n" ::"l"(po.arrived[lane]) : "memory");
-                if (lane < po.world && lane != po.rank) {
-                    const uint64_t t0 = global_ns();
-                    while (true) {
-                        unsigned int seen;
-                        asm volatile("ld.relaxed.sys.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(po.local_arrived + lane) : "memory");
-                        if ((int)(seen - target) >= 0) {
-                            // seen it: read it once more as an acquire, which orders the peer's rows before
-                            // whatever follows this kernel
-                            asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(po.local_arrived + lane) : "memory");
-                            break;
-                        }
-                        if (global_ns() - t0 > 1000000000ull) {
-                            if (status) atomicExch(status, B200HT_ERR_TIMEOUT);
-                            break;
-                        }
+        // Collect: the other ranks' rows arrive in this GPU's slot array (value, tag); every CTA takes an equal share
+        // of them, waits for each tag -- at most a second in all, then B200HT_ERR_TIMEOUT in the status word --
+        // and writes the value into the full result.  No fence and no counter is on this path: a value costs one
+        // trip over the link.  Kernel complete => Y complete.
+        const long own0 = (long)po.row_begin * B, own_n = (long)M * B;
+        const long foreign = (long)po.rows_total * B - own_n;
+        const long per = (foreign + gridDim.x - 1) / gridDim.x;
+        const long i0 = (long)blockIdx.x * per;
+        const long i1 = i0 + per < foreign ? i0 + per : foreign;
+        const uint64_t t0 = global_ns();
+        for (long i = i0 + tid; i < i1; i += GV_THREADS) {
+            const long g = i < own0 ? i : i + own_n;      // position in the full result
+            uint32_t val = 0, seen = 0;
+            uint32_t spins = 0;
+            while (true) {
+                asm volatile("ld.volatile.global.v2.b32 {%0, %1}, [%2];\n" : "=r"(val), "=r"(seen) : "l"(po.my_slots + g) : "memory");
+                if (seen == tag) break;
+                if ((++spins & 63u) == 0) {
+                    if (*abort_flag) break;
+                    if (global_ns() - t0 > 1000000000ull) {
+                        *abort_flag = 1;
+                        if (status) atomicExch(status, B200HT_ERR_TIMEOUT);
+                        break;
                     }
                 }
-                __syncwarp();
             }
+            if (seen == tag) store_out(po.y_full, (size_t)g, __uint_as_float(val), out_dtype);
+        }
+        // count the CTA and, in the last one, the call (one 64-bit word: finished CTAs low, calls high)
+        __syncthreads();
+        if (tid == 0) {
+            const unsigned long long old = atomicAdd((unsigned long long *)po.local_count, 1ull);
+            if ((unsigned int)old + 1u == gridDim.x)
+                asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;\n" ::"l"(po.local_count),
+                             "l"((1ull << 32) - (unsigned long long)gridDim.x)
+                             : "memory");
         }
     }
 }
@@ -950,9 +948,9 @@ extern "C" int b200ht_fused_gemv(const void *W, const void *X, void *Y, int M, i
     return launch_gemv(W, X, Y, M, N, B, in_dtype, out_dtype, scale, (cudaStream_t)stream);
 }
 
-extern "C" int b200ht_fused_gemv_peers(const void *W, const void *X, void *Y, int M, int N, int B, int in_dtype, int out_dtype,
-                                       float scale, int n_peers, void *const *peer_y, unsigned int *const *peer_arrived,
-                                       unsigned int *local_count, const unsigned int *local_arrived, int world, int rank,
+extern "C" int b200ht_fused_gemv_peers(const void *W, const void *X, void *Y_full, int M, int N, int B, int in_dtype,
+                                       int out_dtype, float scale, int row_begin, int rows_total, int n_peers,
+                                       void *const *peer_slots, const void *my_slots, unsigned int *local_count,
                                        unsigned int target, void *stream)
 {
     using namespace b200ht;
@@ -960,25 +958,30 @@ extern "C" int b200ht_fused_gemv_peers(const void *W, const void *X, void *Y, in
     if (out_dtype != B200HT_F32 && out_dtype != B200HT_BF16) return B200HT_ERR_DTYPE;
     if (N < 256 || N > 8192 || !is_pow2((uint64_t)N)) return B200HT_ERR_SIZE;
     if (M < 1 || B < 1 || B > stream_cols_max(N, B)) return B200HT_ERR_SIZE;
-    if (n_peers < 0 || n_peers > 7 || world < 1 || world > 8 || rank < 0 || rank >= world) return B200HT_ERR_SIZE;
-    if (!W || !X || !Y || !local_count || !local_arrived || (n_peers && (!peer_y || !peer_arrived))) return B200HT_ERR_NULL;
-    // Y points into the middle of a result buffer (this rank's first row): element alignment is all it needs
-    if (!aligned16(W) || !aligned16(X) || ((uintptr_t)Y & (out_dtype == B200HT_F32 ? 3u : 1u)) || ((uintptr_t)local_count & 7u))
+    if (n_peers < 0 || n_peers > 7 || row_begin < 0 || rows_total < M || row_begin > rows_total - M) return B200HT_ERR_SIZE;
+    if ((uint64_t)rows_total * (uint64_t)B >= (1ull << 31)) return B200HT_ERR_SIZE;
+    if (!W || !X || !Y_full || !local_count || (n_peers && (!peer_slots || !my_slots))) return B200HT_ERR_NULL;
+    const size_t esz = out_dtype == B200HT_F32 ? 4 : 2;
+    if (!aligned16(W) || !aligned16(X) || ((uintptr_t)Y_full & (esz - 1)) || ((uintptr_t)local_count & 7u) ||
+        ((uintptr_t)my_slots & 7u))
         return B200HT_ERR_ALIGN;
     int rc = check_device();
     if (rc) return rc;
     PeerOut po{};
     po.n = n_peers;
     for (int p = 0; p < n_peers; ++p) {
-        if (!peer_y[p] || !peer_arrived[p]) return B200HT_ERR_NULL;
-        po.y[p] = (unsigned char *)peer_y[p];
-        po.arrived[p] = peer_arrived[p];
+        if (!peer_slots[p]) return B200HT_ERR_NULL;
+        if ((uintptr_t)peer_slots[p] & 7u) return B200HT_ERR_ALIGN;
+        po.slots[p] = (unsigned long long *)peer_slots[p];
     }
+    po.my_slots = (const unsigned long long *)my_slots;
+    po.y_full = Y_full;
     po.local_count = local_count;
-    po.local_arrived = local_arrived;
     po.target = target;
-    po.world = world;
-    po.rank = rank;
+    po.row_begin = row_begin;
+    po.rows_total = rows_total;
+    // this rank's rows go straight into their place in the full result
+    void *Y = (unsigned char *)Y_full + (size_t)row_begin * B * esz;
     return launch_stream(W, X, Y, M, N, ilog2((uint32_t)N), B, 0, B, out_dtype, scale, (cudaStream_t)stream, po);
 }
 

@@ -97,19 +97,21 @@ class RowShardedGemv:
     kernel's own stores.
 
     Every rank keeps ``shard_rows(W)`` and the same X.  The GEMV kernel writes its rows of Y into its own result
-    buffer and, through peer-mapped pointers, into every other rank's; a per-rank arrival counter tells a rank when
-    all rows of a call have landed (``b200ht_fused_gemv_peers``).  There is no collective on the path: at W 4096 x
-    4096 an NCCL all-gather of the 64 KB result costs several times the kernel.
+    buffer and sends every value, together with the number of the call, as one 8-byte store into a slot array on
+    each other rank (peer-mapped pointers); its CTAs then collect the other ranks' rows from the local slot array,
+    waiting for each slot's tag (``b200ht_fused_gemv_peers``).  There is no collective, no fence and no flag on the
+    path: at W 4096 x 4096 an NCCL all-gather of the 64 KB result costs several times the kernel.
 
-    Set-up (once): each rank allocates one exchange buffer -- two result buffers used alternately plus the counters
-    -- exports it (CUDA IPC), the handles go round with ``all_gather_object`` and every rank maps the others'.
+    Set-up (once): each rank allocates one exchange buffer -- two result buffers and two slot arrays used
+    alternately, plus the kernel's counter word -- exports it (CUDA IPC), the handles go round with
+    ``all_gather_object`` and every rank maps the others'.
     ``__call__`` returns a view of the result buffer of this call; it stays valid until the call after next.  All
     ranks must make the same sequence of calls.  bf16, 256 <= N <= 8192, B <= ``max_batch``.
 
     The kernel counts the calls of an exchange on the device, so no argument changes from one call to the next and
     a CUDA graph can replay calls (which takes the host's launch pace and jitter, the larger part of a call's time
     on 4 and 8 GPUs, out of the loop).  A captured graph must hold an even number of calls of each op: the two
-    result buffers alternate.
+    result buffers and slot arrays alternate.
     """
 
     def __init__(self, W_local: torch.Tensor, n_rows: int, max_batch: int, *, out_dtype: torch.dtype = torch.float32,
@@ -131,9 +133,10 @@ class RowShardedGemv:
         self._plans = {}
         esz = 4 if out_dtype == torch.float32 else 2
         self.y_bytes = (self.n_rows * self.max_batch * esz + 255) & ~255
+        self.slot_bytes = (self.n_rows * self.max_batch * 8 + 255) & ~255
         self.backend = backend if backend is not None else _IpcBackend(W_local.device)
-        # exchange buffer: [counters: 256 bytes][result buffer 0][result buffer 1]
-        self.buf = self.backend.allocate(256 + 2 * self.y_bytes)
+        # exchange buffer (zeroed): [counter word: 256 bytes][result 0][result 1][slot array 0][slot array 1]
+        self.buf = self.backend.allocate(256 + 2 * self.y_bytes + 2 * self.slot_bytes)
         handle = self.backend.export(self.buf)
         handles = [None] * self.world
         dist.all_gather_object(handles, handle, group=group)
@@ -144,33 +147,31 @@ class RowShardedGemv:
         dist.barrier(group=group)   # every rank has zeroed and mapped its buffers before the first call
 
     # layout of the exchange buffer
-    def _arrived(self, base: int, src_rank: int) -> int:
-        return base + 4 * src_rank             # arrival counter of rank src_rank
     def _local_count(self, base: int) -> int:
         return base + 128                      # kernel scratch word, then the kernel's count of calls
-    def _rows(self, base: int, parity: int, row: int, batch: int, esz: int) -> int:
-        return base + 256 + parity * self.y_bytes + row * batch * esz
+    def _result(self, base: int, parity: int) -> int:
+        return base + 256 + parity * self.y_bytes
+    def _slots(self, base: int, parity: int) -> int:
+        return base + 256 + 2 * self.y_bytes + parity * self.slot_bytes
 
     def plan(self, batch: int) -> dict:
         """Addresses and number of the NEXT call (also what the host-side tests check)."""
         if not (1 <= batch <= self.max_batch):
             raise RuntimeError(f"RowShardedGemv: batch must be in [1, {self.max_batch}]")
         parity = self.calls & 1
-        p = self._plans.get((batch, parity))
+        p = self._plans.get(parity)
         if p is None:
-            esz = 4 if self.out_dtype == torch.float32 else 2
             mine = self.bases[self.rank]
             p = {
                 "parity": parity,
-                "y_local": self._rows(mine, parity, self.row_begin, batch, esz),
-                "peer_y": [self._rows(self.bases[r], parity, self.row_begin, batch, esz) for r in self.peers],
-                "peer_arrived": [self._arrived(self.bases[r], self.rank) for r in self.peers],
+                "y_full": self._result(mine, parity),
+                "my_slots": self._slots(mine, parity),
+                "peer_slots": [self._slots(self.bases[r], parity) for r in self.peers],
                 "local_count": self._local_count(mine),
-                "local_arrived": self._arrived(mine, 0),
-                "y_full": self._rows(mine, parity, 0, batch, esz),
+                "views": {},
             }
-            self._plans[(batch, parity)] = p
-        p["call"] = self.calls + 1      # the value the arrival counters reach with this call (the kernel keeps its own count)
+            self._plans[parity] = p
+        p["call"] = self.calls + 1      # the tag of this call's values (the kernel keeps its own count)
         return p
 
     def __call__(self, X: torch.Tensor, *, scale: float | None = None) -> torch.Tensor:
@@ -182,10 +183,10 @@ class RowShardedGemv:
             X = X.contiguous()
         self.backend.launch(self, X, batch, p, scale)
         self.calls += 1
-        y = p.get("view")
+        y = p["views"].get(batch)
         if y is None:
             y = self.backend.view(self.buf, p["y_full"] - self.bases[self.rank], (self.n_rows, batch), self.out_dtype)
-            p["view"] = y
+            p["views"][batch] = y
         return y
 
     def close(self) -> None:
@@ -241,23 +242,22 @@ class _IpcBackend:
     def launch(self, op: "RowShardedGemv", X: torch.Tensor, batch: int, p: dict, scale) -> None:
         import ctypes
         import math
-        # the pointer arrays of a (batch, parity) pair never change: build them once
-        key = (id(op), batch, p["parity"])
+        # the pointer array of a parity never changes: build it once
+        key = (id(op), p["parity"])
         args = self._args.get(key)
         if args is None:
-            n = len(p["peer_y"])
+            n = len(p["peer_slots"])
             vp = ctypes.c_void_p
             dt = {torch.float32: self._lib.F32, torch.bfloat16: self._lib.BF16}
-            args = ((vp * max(n, 1))(*p["peer_y"]), (vp * max(n, 1))(*p["peer_arrived"]), n, dt[op.W.dtype],
-                    dt[op.out_dtype], math.sqrt(1.0 / op.N))
+            args = ((vp * max(n, 1))(*p["peer_slots"]), n, dt[op.W.dtype], dt[op.out_dtype], math.sqrt(1.0 / op.N))
             self._args[key] = args
-        peer_y, peer_arrived, n, in_dt, out_dt, default_scale = args
+        peer_slots, n, in_dt, out_dt, default_scale = args
         sc = default_scale if scale is None else scale
 
         def enqueue():
             return self.lib.b200ht_fused_gemv_peers(
-                op.W.data_ptr(), X.data_ptr(), p["y_local"], op.row_end - op.row_begin, op.N, batch, in_dt, out_dt,
-                float(sc), n, peer_y, peer_arrived, p["local_count"], p["local_arrived"], op.world, op.rank,
+                op.W.data_ptr(), X.data_ptr(), p["y_full"], op.row_end - op.row_begin, op.N, batch, in_dt, out_dt,
+                float(sc), op.row_begin, op.n_rows, n, peer_slots, p["my_slots"], p["local_count"],
                 0, torch.cuda.current_stream(self.device).cuda_stream)   # 0: calls counted on the device
 
         # (switching the device costs more host time than the call; one process per GPU is already on it)

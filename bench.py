@@ -291,9 +291,10 @@ def time_gemv(pkg, torch, peaks, reps=20):
 
 
 def time_gemv_rows(pkg, torch, dist, rank, world, reps=20):
-    """Row-sharded small-batch GEMV (world > 1): every rank keeps M/world rows of W, computes its rows of Y and stores
-    them into every rank's result buffer through peer-mapped pointers (RowShardedGemv: no collective; a counter per
-    rank tells when a call is complete).  Timed per call, 8 rotating copies of the W shard, B = 4; W 4096 x 4096 (the
+    """Row-sharded small-batch GEMV (world > 1): every rank keeps M/world rows of W, computes its rows of Y and sends
+    them, tagged with the number of the call, into a slot array on every other rank through peer-mapped pointers; the
+    same kernel collects the other ranks' rows (RowShardedGemv: no collective, no fence, no flag).  Timed per call,
+    launched from the host and replayed from a CUDA graph, 8 rotating copies of the W shard, B = 4; W 4096 x 4096 (the
     C4 shape) and 28672 x 8192 (the C5 weight).  `parity`: rank 0 compares the assembled Y of one call with the
     single-GPU call on the full W (same seeded data on every rank).  `nccl_ms` is the same split with an NCCL
     all-gather of Y after a plain GEMV, for comparison."""
@@ -368,7 +369,7 @@ def time_gemv_rows(pkg, torch, dist, rank, world, reps=20):
                            "parity": bool(parity.item()) and status == 0, "rel_err_vs_one_gpu": err,
                            "graph_replay_ms": graph_ms, "gbs_all_gpus_graph": M * N * 2 / (graph_ms * 1e-3) / 1e9,
                            "nccl_all_gather_ms": nccl_ms, "host_enqueue_ms": host_ms,
-                           "exchange": "peer stores + arrival counters"}
+                           "exchange": "peer stores of (value, call number) slots, collected by the kernel"}
         for op in ops:
             op.close()
         del Ws, ops

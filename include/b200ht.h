@@ -193,31 +193,32 @@ int b200ht_fused_gemv_max_batch(int N, int in_dtype);
 
 /*
  * Row-sharded small-batch GEMV across the GPUs of one node (one process per GPU).  Every rank keeps M rows of W (its
- * shard) and the same X; the kernel writes its M x B results into its own Y and, through peer-mapped pointers, into
- * the Y buffers of the other ranks, so that after the call every rank holds all rows: the exchange is part of the
- * kernel's stores, not a separate collective.  No counterpart in the reference, which is single-GPU.
- *   Y             this rank's rows inside its own full result buffer (16-byte aligned)
- *   peer_y[p]     the same position inside peer p's full result buffer (n_peers <= 7 pointers valid on this GPU,
- *                 e.g. from b200ht_ipc_open)
- *   peer_arrived[p]  address, in peer p's memory, of the 32-bit arrival counter that belongs to THIS rank
- *   local_count   two zero-initialised 32-bit words in this GPU's memory, 8-byte aligned (the kernel updates them
- *                 as one 64-bit word): [0] scratch, left at zero; [1] calls made so far, counted by the kernel
- *   local_arrived this GPU's array of `world` arrival counters (zero-initialised once; entry `rank` is unused)
- *   target        number of calls made so far on this exchange, this one included: all ranks call in lockstep.
- *                 0 = take it from local_count[1]: no argument then changes from call to call, so a CUDA graph can
- *                 replay the call (use one way of counting per exchange, not both)
- * The last CTA of the kernel to finish waits, for at most one second, until every other rank's counter has reached
- * `target`; work enqueued behind the call sees the complete Y.  If a peer never arrives the wait gives up, the status
- * word (b200ht_device_status) reports B200HT_ERR_TIMEOUT and nothing hangs.  A rank must not start call k + 2 before
- * its consumers of call k's result are enqueued: alternate between two result buffers (the Python wrapper does).
- * BF16 inputs, 256 <= N <= 8192, B <= b200ht_fused_gemv_max_batch(N, B200HT_BF16); other shapes return
- * B200HT_ERR_SIZE (gather the shards with a collective instead).
+ * shard: rows row_begin .. row_begin + M - 1 of the rows_total rows of the full matrix) and the same X; after the call
+ * every rank holds all rows of Y = W . H(X).  The exchange is part of the kernel: it writes its own rows into Y_full
+ * and sends each value, as one 8-byte store (value, number of the call), into a slot array on every other rank
+ * through peer-mapped pointers; then its CTAs collect the other ranks' rows from this GPU's slot array, waiting for
+ * each slot's tag, and write them into Y_full.  No collective, no fence and no flag on the path: a value costs one
+ * trip over the link.  No counterpart in the reference, which is single-GPU.
+ *   Y_full        this rank's full result, rows_total x B values of out_dtype
+ *   peer_slots[p] the slot array in peer p's memory (n_peers <= 7 pointers valid on this GPU, e.g. from
+ *                 b200ht_ipc_open), rows_total x B slots of 8 bytes, zero-initialised once
+ *   my_slots      this GPU's slot array, of the same size (the peers write it)
+ *   local_count   two zero-initialised 32-bit words in this GPU's memory, 8-byte aligned (the kernel updates them as
+ *                 one 64-bit word): [0] scratch, left at zero; [1] calls made so far, counted by the kernel
+ *   target        number of this call on this exchange, 1, 2, 3, ...: all ranks call in lockstep.  0 = take it from
+ *                 local_count[1]: no argument then changes from call to call, so a CUDA graph can replay the call
+ *                 (use one way of counting per exchange, not both)
+ * A rank waits at most one second for the other ranks' values; if one never arrives the status word
+ * (b200ht_device_status) reports B200HT_ERR_TIMEOUT and nothing hangs.  A rank must not start call k + 2 before its
+ * consumers of call k's result are enqueued, and slots are reused every second call: alternate between two result
+ * buffers and two slot arrays (the Python wrapper does).
+ * BF16 inputs, 256 <= N <= 8192, B <= b200ht_fused_gemv_max_batch(N, B200HT_BF16), rows_total * B < 2^31; other
+ * shapes return B200HT_ERR_SIZE (gather the shards with a collective instead).
  */
-int b200ht_fused_gemv_peers(const void *W, const void *X, void *Y, int M, int N, int B, int in_dtype,
-                            int out_dtype, float scale, int n_peers, void *const *peer_y,
-                            unsigned int *const *peer_arrived, unsigned int *local_count,
-                            const unsigned int *local_arrived, int world, int rank, unsigned int target,
-                            void *stream);
+int b200ht_fused_gemv_peers(const void *W, const void *X, void *Y_full, int M, int N, int B, int in_dtype,
+                            int out_dtype, float scale, int row_begin, int rows_total, int n_peers,
+                            void *const *peer_slots, const void *my_slots, unsigned int *local_count,
+                            unsigned int target, void *stream);
 
 /*
  * Inter-process mapping of device buffers for b200ht_fused_gemv_peers: b200ht_ipc_export writes a 64-byte handle for

@@ -175,9 +175,9 @@ def test_two_rank_gloo_row_sharded_gemv(tmp_path):
 
 def test_two_rank_gloo_peer_store_gemv_bookkeeping(tmp_path):
     """Host side of the peer-store row-sharded GEMV, two gloo ranks on the CPU with a stand-in for the CUDA side:
-    the handle exchange gives every rank the other ranks' buffers (never its own as a peer), this rank's rows land at
-    the same offset in every buffer, the arrival counter a rank bumps on a peer is the peer's slot for THAT rank,
-    the counter target grows by one per call and the two result buffers alternate."""
+    the handle exchange gives every rank the other ranks' buffers (never its own as a peer), the slot array a rank
+    sends into sits at the same offset in every buffer and is the one the peer reads for that call, results and
+    slot arrays do not overlap, the number of the call grows by one per call and the two buffers alternate."""
     script = tmp_path / "worker.py"
     script.write_text(textwrap.dedent(f"""
         import importlib, sys
@@ -211,11 +211,14 @@ def test_two_rank_gloo_peer_store_gemv_bookkeeping(tmp_path):
             assert y.shape == (M, B)
             assert plan["call"] == call + 1 and plan["parity"] == call % 2
             mine, peer = 1000000 * (rank + 1), 1000000 * (other + 1)
-            row_off = 256 + (call % 2) * op.y_bytes + a * B * 4
-            assert plan["y_local"] == mine + row_off and plan["peer_y"] == [peer + row_off]
-            assert plan["peer_arrived"] == [peer + 4 * rank]          # my counter in the peer's array
-            assert plan["local_arrived"] == mine and plan["local_count"] == mine + 128
-            assert plan["y_full"] == mine + 256 + (call % 2) * op.y_bytes
+            par = call % 2
+            assert plan["local_count"] == mine + 128 and plan["local_count"] % 8 == 0
+            assert plan["y_full"] == mine + 256 + par * op.y_bytes
+            slot_off = 256 + 2 * op.y_bytes + par * op.slot_bytes
+            assert plan["my_slots"] == mine + slot_off and plan["peer_slots"] == [peer + slot_off]
+            assert plan["my_slots"] % 8 == 0 and op.slot_bytes >= M * 4 * 8 and op.y_bytes >= M * 4 * 4
+            # the two results and the two slot arrays tile the buffer behind the counter word
+            assert slot_off + op.slot_bytes <= op.backend.nbytes and 256 + (par + 1) * op.y_bytes <= 256 + 2 * op.y_bytes
         try:
             op(torch.zeros(N, 5, dtype=torch.bfloat16))
             raise SystemExit("batch beyond max_batch was accepted")

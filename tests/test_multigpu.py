@@ -84,8 +84,9 @@ def test_two_gpu_row_sharded_gemv(tmp_path):
 
 @pytest.mark.gpu
 def test_two_gpu_row_sharded_gemv_with_peer_stores(tmp_path):
-    """The same split with the exchange inside the kernel: every GPU stores its rows of Y into both result buffers
-    through peer-mapped pointers and a counter per rank says when a call is complete.  Several calls back to back
+    """The same split with the exchange inside the kernel: every GPU sends its rows of Y, tagged with the number of
+    the call, into a slot array on the other GPU through peer-mapped pointers and collects the other's rows from its
+    own.  Several calls back to back
     (the two result buffers alternate), ragged row split, both output types; compared with the single-GPU call."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
