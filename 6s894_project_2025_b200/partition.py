@@ -206,6 +206,9 @@ class _IpcBackend:
         self.lib = _lib.load()
         self._opened = {}
         self._args = {}
+        # the current stream's handle, by the shortest route torch offers (the call is short enough for this to show)
+        self._raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None) or (
+            lambda index: torch.cuda.current_stream(index).cuda_stream)
 
     def allocate(self, nbytes: int) -> torch.Tensor:
         # a private cudaMalloc block (IPC handles cover whole allocations): bypass the caching allocator's pooling
@@ -249,16 +252,17 @@ class _IpcBackend:
             n = len(p["peer_slots"])
             vp = ctypes.c_void_p
             dt = {torch.float32: self._lib.F32, torch.bfloat16: self._lib.BF16}
-            args = ((vp * max(n, 1))(*p["peer_slots"]), n, dt[op.W.dtype], dt[op.out_dtype], math.sqrt(1.0 / op.N))
+            args = ((vp * max(n, 1))(*p["peer_slots"]), n, dt[op.W.dtype], dt[op.out_dtype], math.sqrt(1.0 / op.N),
+                    op.W.data_ptr())
             self._args[key] = args
-        peer_slots, n, in_dt, out_dt, default_scale = args
+        peer_slots, n, in_dt, out_dt, default_scale, w_ptr = args
         sc = default_scale if scale is None else scale
 
         def enqueue():
             return self.lib.b200ht_fused_gemv_peers(
-                op.W.data_ptr(), X.data_ptr(), p["y_full"], op.row_end - op.row_begin, op.N, batch, in_dt, out_dt,
+                w_ptr, X.data_ptr(), p["y_full"], op.row_end - op.row_begin, op.N, batch, in_dt, out_dt,
                 float(sc), op.row_begin, op.n_rows, n, peer_slots, p["my_slots"], p["local_count"],
-                0, torch.cuda.current_stream(self.device).cuda_stream)   # 0: calls counted on the device
+                0, self._raw_stream(self.index))   # 0: calls counted on the device
 
         # (switching the device costs more host time than the call; one process per GPU is already on it)
         if torch.cuda.current_device() == self.index:
