@@ -163,8 +163,10 @@ gemv_bf16_kernel(const __nv_bfloat16 *W, const __nv_bfloat16 *X, void *Y, int M,
 // ---------------------------------------------------------------------------
 constexpr int GV_WARPS = 16;
 constexpr int GV_THREADS = GV_WARPS * 32;
-constexpr int GV_GROUPS = 4;                         // warp groups of the consume phase
-constexpr int GV_GW = GV_WARPS / GV_GROUPS;          // warps per group
+// The consume phase runs in warp groups of GW warps (template parameter of the kernel), each on a ring item of its
+// own: four groups of four when a CTA has one row group (a short call: more items in work at once), two groups of
+// eight when it has several (a long stream: fewer stages held by consumers, more of the ring in flight -- 5.9
+// against 4.6 TB/s at 14336 x 8192, the other way round at 4096 x 4096).
 constexpr int GV_MAX_GROUP_ROWS = 32;                // rows of W per ring stage (one or two 16-row tiles)
 
 __host__ __device__ constexpr int hxt_pitch(int N) { return N * 2 + 16; }   // bytes per column of H(X)
@@ -287,7 +289,7 @@ struct PeerOut {
     int row_begin, rows_total;          // this rank's first row in the full result, rows of the full result
 };
 
-template <int NT>
+template <int NT, int GW>
 __global__ void __launch_bounds__(GV_THREADS, 1)
 gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bfloat16 *X, void *Y, int M, int N,
                         int logn, int B, int b0, int Bg, int out_dtype, float scale, int rows_per_cta,
@@ -507,7 +509,8 @@ gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bflo
     const int g = lane >> 2, t = lane & 3;
     const uint32_t hx_s = smem_u32(hxT);
     const int rt = group_rows > 16 ? 2 : 1;               // 16-row tiles per row group
-    const int wg = warp / GV_GW, wj = warp - wg * GV_GW;   // warp group, warp within the group
+    constexpr int GROUPS = GV_WARPS / GW;
+    const int wg = warp / GW, wj = warp - wg * GW;   // warp group, warp within the group
     // ldmatrix (A): lane -> (row, 16-byte k chunk) of a 16 x 16 block, 128-byte swizzle of the TMA tile
     const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8;
     const int a_chunk = lane >> 4;
@@ -533,18 +536,18 @@ gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bflo
         // of groups: a stage is always consumed by the same group, so its warps see every phase of its barrier
         // (a one-bit phase parity cannot tell "not yet filled" from "filled twice since").
         const int first = grp * nchunks;
-        for (int item = first + ((wg - first) & (GV_GROUPS - 1)); item < first + nchunks; item += GV_GROUPS) {
+        for (int item = first + ((wg - first) & (GROUPS - 1)); item < first + nchunks; item += GROUPS) {
             const int chunk = item - first;
             const int s = item % nstages;
             const uint32_t ph = (uint32_t)(item / nstages) & 1u;
             if (!mbar_wait(full_bar(s), ph, abort_flag, status)) return;
             const uint32_t stage = ring_s + (uint32_t)(s * stage_bytes);
             // this warp's k steps of the item, UNR at a time: all fragment loads first, then the products
-            for (int ks0 = wj; ks0 < ksteps; ks0 += GV_GW * UNR) {
+            for (int ks0 = wj; ks0 < ksteps; ks0 += GW * UNR) {
                 uint32_t a[UNR][2][4], b[UNR][NT][2];
 #pragma unroll
                 for (int u = 0; u < UNR; ++u) {
-                    const int ks = ks0 + u * GV_GW;
+                    const int ks = ks0 + u * GW;
                     if (ks < ksteps) {
                         const int c = ks >> 2, ks4 = ks & 3;
 #pragma unroll
@@ -565,7 +568,7 @@ gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bflo
                 }
 #pragma unroll
                 for (int u = 0; u < UNR; ++u) {
-                    if (ks0 + u * GV_GW < ksteps) {
+                    if (ks0 + u * GW < ksteps) {
 #pragma unroll
                         for (int h = 0; h < 2; ++h) {
                             if (h < rt) {
@@ -584,7 +587,7 @@ gemv_bf16_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __nv_bflo
             if (lane == 0) {
                 __threadfence_block();
                 const int done = atomicAdd(&released[s], 1);   // counts up over all uses of the stage
-                if ((done & (GV_GW - 1)) == GV_GW - 1 && item + nstages < total_items) issue(item + nstages);
+                if ((done & (GW - 1)) == GW - 1 && item + nstages < total_items) issue(item + nstages);
             }
         }
         // row group finished: reduce the 16 warps' partial sums through shared memory, upper half first
@@ -793,6 +796,8 @@ static int launch_stream_nt(const void *W, const void *X, void *Y, int M, int N,
     grid = (M + rows_per_cta - 1) / rows_per_cta;
     const int groups = (rows_per_cta + GV_MAX_GROUP_ROWS - 1) / GV_MAX_GROUP_ROWS;
     const int group_rows = (rows_per_cta + groups - 1) / groups;
+    // warp groups of the consume phase: four of four warps for a CTA with one row group, two of eight otherwise
+    const int wgroups = groups == 1 ? 4 : 2;
     // One TMA op = group_rows x (64*kc) elements, at most 32 KB, kc a power of two dividing N/64.  The number of
     // stages is a multiple of the number of warp groups (see the kernel); among the candidates take the one that
     // keeps most bytes in flight, preferring at least one item per warp group and then the larger op.
@@ -805,9 +810,9 @@ static int launch_stream_nt(const void *W, const void *X, void *Y, int M, int N,
             if ((N / 64) % cand || (size_t)group_rows * 128 * cand > 32 * 1024) continue;
             const int sb = ((group_rows * 128 * cand) + 1023) & ~1023;
             int st = (int)(ring_room / sb);
-            st = (st > 16 ? 16 : st) & ~(GV_GROUPS - 1);
-            if (st < GV_GROUPS) continue;
-            const size_t score = (size_t)st * sb + ((N / 64) / cand >= GV_GROUPS ? (size_t)1 << 30 : 0);
+            st = (st > 16 ? 16 : st) & ~(wgroups - 1);
+            if (st < wgroups) continue;
+            const size_t score = (size_t)st * sb + ((N / 64) / cand >= wgroups ? (size_t)1 << 30 : 0);
             if (score > best) { best = score; kc = cand; stages = st; stage_bytes = sb; }
         }
     };
@@ -823,11 +828,12 @@ static int launch_stream_nt(const void *W, const void *X, void *Y, int M, int N,
     CUtensorMap tw;
     int rc = encode_tmap_bf16_rows_chunks(&tw, W, (uint64_t)M, (uint64_t)N, (uint32_t)group_rows, (uint32_t)kc);
     if (rc) return rc;
-    rc = ensure_dyn_smem((const void *)gemv_bf16_stream_kernel<NT>, (int)smem);
+    auto kernel = wgroups == 4 ? gemv_bf16_stream_kernel<NT, GV_WARPS / 4> : gemv_bf16_stream_kernel<NT, GV_WARPS / 2>;
+    rc = ensure_dyn_smem((const void *)kernel, (int)smem);
     if (rc) return rc;
-    return launch_pdl(gemv_bf16_stream_kernel<NT>, dim3(grid), dim3(GV_THREADS), smem, st, tw,
-                      (const __nv_bfloat16 *)X, Y, M, N, logn, B, b0, Bg, out_dtype, scale, rows_per_cta, group_rows, kc,
-                      stage_bytes, stages, red_in_ring ? 1 : 0, status_word_ptr(), po);
+    return launch_pdl(kernel, dim3(grid), dim3(GV_THREADS), smem, st, tw, (const __nv_bfloat16 *)X, Y, M, N, logn, B, b0,
+                      Bg, out_dtype, scale, rows_per_cta, group_rows, kc, stage_bytes, stages, red_in_ring ? 1 : 0,
+                      status_word_ptr(), po);
 }
 
 static int launch_stream(const void *W, const void *X, void *Y, int M, int N, int logn, int B, int b0, int Bg,
