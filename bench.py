@@ -287,6 +287,30 @@ def time_gemv(pkg, torch, peaks, reps=20):
         nbytes = M * N * 2 + N * B * 2 + M * B * 4
         gbs = nbytes / (ms * 1e-3) / 1e9
         out[str(B)] = {"ms": ms, "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"]}
+    del Ws
+    # the same call on a large weight (the C5 matrix, 28672 x 8192 = 470 MB, two rotating copies), B = 4: a long
+    # stream instead of a 9 us call
+    M, N, B = 28672, 8192, 4
+    Ws = [(torch.randn(M, N, generator=g, device="cuda") / 90).bfloat16() for _ in range(2)]
+    X = torch.randn(N, B, generator=g, device="cuda").bfloat16()
+    Y = torch.empty(M, B, dtype=torch.float32, device="cuda")
+    for Wt in Ws * 2:
+        rc = lib.b200ht_fused_gemv(Wt.data_ptr(), X.data_ptr(), Y.data_ptr(), M, N, B, pkg._lib.BF16, pkg._lib.F32,
+                                   float(N ** -0.5), st)
+        if rc:
+            raise RuntimeError(pkg._lib.error_string(rc))
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        for Wt in Ws:
+            lib.b200ht_fused_gemv(Wt.data_ptr(), X.data_ptr(), Y.data_ptr(), M, N, B, pkg._lib.BF16, pkg._lib.F32,
+                                  float(N ** -0.5), st)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / (reps * len(Ws))
+    gbs = (M * N * 2 + N * B * 2 + M * B * 4) / (ms * 1e-3) / 1e9
+    out["28672x8192_b4"] = {"ms": ms, "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"]}
     return out
 
 
