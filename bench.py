@@ -843,6 +843,13 @@ def run_profile_case(case: str):
             torch.cuda.synchronize()
             print("fwht-sweep case", n, nbuf, float(bufs[0].float().abs().mean()))
             del bufs
+    elif case == "gemv-large":   # fused GEMV on the C5 weight, 28672 x 8192 bf16 (470 MB), B = 4, two rotating copies
+        Ws = [(torch.randn(28672, 8192, generator=g, device="cuda") / 90).bfloat16() for _ in range(2)]
+        X = torch.randn(8192, 4, generator=g, device="cuda").bfloat16()
+        for _ in range(3):
+            for W in Ws:
+                Y = pkg.fused_ht_gemv(W, X)
+        print("gemv-large case", float(Y.abs().mean()))
     else:                   # fused GEMV, W 4096 x 4096 bf16, B = 16 and 1, distinct W buffers
         Ws = [(torch.randn(4096, 4096, generator=g, device="cuda") / 64).bfloat16() for _ in range(6)]
         for B in (16, 1):
@@ -995,7 +1002,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--profile-case", default=None, choices=["gemm", "gemm-full", "fwht", "fwht-sweep", "gemv", "c3"],
+    ap.add_argument("--profile-case", default=None, choices=["gemm", "gemm-full", "fwht", "fwht-sweep", "gemv", "gemv-large", "c3"],
                     help="run a few launches of ONE kernel on a reduced shape and exit (for ncu captures)")
     ap.add_argument("--compare", default=None, choices=["cublas", "orders"],
                     help="time library comparators beside this repository's calls on one GPU and exit")
