@@ -28,6 +28,43 @@ def test_bounded_wait_gives_up_and_context_survives(pkg, lib):
     assert pkg.device_status() == 0
 
 
+@pytest.mark.gpu
+def test_row_sharded_gemv_gives_up_on_a_peer_that_never_sends(pkg, lib):
+    """The one cross-GPU wait of the library, run out on one GPU: a row-sharded GEMV call whose "peer" is a slot array
+    that nothing fills.  The kernel computes its own rows, waits a second for the other half, gives up with
+    B200HT_ERR_TIMEOUT in the status word, and the context keeps working."""
+    import ctypes
+    l = lib.load()
+    assert l.b200ht_device_status(1) == 0
+    M, N, B = 512, 1024, 4
+    g = torch.Generator(device="cuda").manual_seed(11)
+    W = (torch.randn(M, N, generator=g, device="cuda") / 32).bfloat16()
+    X = torch.randn(N, B, generator=g, device="cuda").bfloat16()
+    half = M // 2
+    y_full = torch.full((M, B), 7.0, device="cuda")
+    my_slots = torch.zeros(M * B, dtype=torch.int64, device="cuda")       # the peer would write here; nobody does
+    peer_slots = torch.zeros(M * B, dtype=torch.int64, device="cuda")     # stands in for the peer's memory
+    count = torch.zeros(2, dtype=torch.int32, device="cuda")
+    peers = (ctypes.c_void_p * 1)(peer_slots.data_ptr())
+    torch.cuda.synchronize()
+    rc = l.b200ht_fused_gemv_peers(W.data_ptr(), X.data_ptr(), y_full.data_ptr(), half, N, B, lib.BF16, lib.F32,
+                                   float(N ** -0.5), 0, M, 1, peers, my_slots.data_ptr(), count.data_ptr(), 1,
+                                   torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, lib.error_string(rc)
+    torch.cuda.synchronize()
+    assert l.b200ht_device_status(1) == -8
+    # its own rows are there, the other half was never touched, and the values it sent carry the call's number
+    ref = pkg.fused_ht_gemv(W[:half], X)
+    assert torch.equal(y_full[:half], ref)
+    assert bool((y_full[half:] == 7.0).all())
+    sent = peer_slots[: half * B].view(torch.int32).view(-1, 2)          # (value bits, tag) per slot
+    assert bool((sent[:, 1] == 1).all())
+    assert torch.equal(sent[:, 0].contiguous().view(torch.float32).view(half, B), ref)
+    assert bool((peer_slots[half * B:] == 0).all())
+    assert int(count[0]) == 0 and int(count[1]) == 1          # scratch word back at zero, one call counted
+    assert pkg.device_status() == 0
+
+
 def test_missing_rank_is_detected_by_the_survivor(tmp_path):
     """Two gloo ranks; rank 1 exits between steps (never joins the second gather).  Rank 0's collective ends with an
     error after the short process-group timeout instead of hanging."""
