@@ -164,9 +164,8 @@ gemv_bf16_kernel(const __nv_bfloat16 *W, const __nv_bfloat16 *X, void *Y, int M,
 constexpr int GV_WARPS = 16;
 constexpr int GV_THREADS = GV_WARPS * 32;
 // The consume phase runs in warp groups of GW warps (template parameter of the kernel), each on a ring item of its
-// own: four groups of four when a CTA has one row group (a short call: more items in work at once), two groups of
-// eight when it has several (a long stream: fewer stages held by consumers, more of the ring in flight -- 5.9
-// against 4.6 TB/s at 14336 x 8192, the other way round at 4096 x 4096).
+// own: four groups of four, or two groups of eight for a long stream with 8 x 64 k per item (the host's plan says
+// which and why).
 constexpr int GV_MAX_GROUP_ROWS = 32;                // rows of W per ring stage (one or two 16-row tiles)
 
 __host__ __device__ constexpr int hxt_pitch(int N) { return N * 2 + 16; }   // bytes per column of H(X)
@@ -796,17 +795,22 @@ static int launch_stream_nt(const void *W, const void *X, void *Y, int M, int N,
     grid = (M + rows_per_cta - 1) / rows_per_cta;
     const int groups = (rows_per_cta + GV_MAX_GROUP_ROWS - 1) / GV_MAX_GROUP_ROWS;
     const int group_rows = (rows_per_cta + groups - 1) / groups;
-    // warp groups of the consume phase: four of four warps for a CTA with one row group, two of eight otherwise
-    const int wgroups = groups == 1 ? 4 : 2;
     // One TMA op = group_rows x (64*kc) elements, at most 32 KB, kc a power of two dividing N/64.  The number of
-    // stages is a multiple of the number of warp groups (see the kernel); among the candidates take the one that
-    // keeps most bytes in flight, preferring at least one item per warp group and then the larger op.
+    // stages is a multiple of the number of warp groups (see the kernel).
+    //   * A CTA with one row group (a short call): four groups of four warps; among the candidates take the one
+    //     that keeps most bytes in flight, preferring at least one item per warp group and then the larger op.
+    //   * A CTA with several row groups (a long stream): what counts is that a warp gets one unrolled batch of four
+    //     k steps per item, i.e. kc = warps per group, and 1 KB of every row per op rather than 512 bytes: two
+    //     groups of eight warps with kc = 8 if that fits, else four of four with kc = 4.  (28672 x 8192, B = 4:
+    //     6.4 TB/s so; 5.9 with kc = 4 under two groups, 4.6-5.6 with kc = 2.)
+    int wgroups = 4, only_kc = 0;
     int kc = 0, stages = 0, stage_bytes = 0;
     auto plan = [&](bool red_in_ring) {
         const size_t ring_room = kStreamSmemLimit - stream_fixed_smem(N, Bg, red_in_ring);
         size_t best = 0;
         kc = 0;
         for (int cand = 16; cand >= 1; cand >>= 1) {
+            if (only_kc && cand != only_kc) continue;
             if ((N / 64) % cand || (size_t)group_rows * 128 * cand > 32 * 1024) continue;
             const int sb = ((group_rows * 128 * cand) + 1023) & ~1023;
             int st = (int)(ring_room / sb);
@@ -818,10 +822,21 @@ static int launch_stream_nt(const void *W, const void *X, void *Y, int M, int N,
     };
     // the reduction buffer reuses the start of the ring when it runs once, at the end, and fits there
     bool red_in_ring = groups == 1;
-    plan(red_in_ring);
-    if (red_in_ring && (!kc || (size_t)stages * stage_bytes < (size_t)(GV_WARPS / 2) * 32 * NT * 8 * 4)) {
-        red_in_ring = false;
+    if (groups > 1) {
+        wgroups = 2, only_kc = 8;
         plan(false);
+        if (!kc) {
+            wgroups = 4, only_kc = 4;
+            plan(false);
+        }
+        if (!kc) only_kc = 0;      // neither fits: any plan will do
+    }
+    if (!kc) {
+        plan(red_in_ring);
+        if (red_in_ring && (!kc || (size_t)stages * stage_bytes < (size_t)(GV_WARPS / 2) * 32 * NT * 8 * 4)) {
+            red_in_ring = false;
+            plan(false);
+        }
     }
     if (!kc) return B200HT_ERR_SIZE;
     const size_t smem = stream_fixed_smem(N, Bg, red_in_ring) + (size_t)stages * stage_bytes;
