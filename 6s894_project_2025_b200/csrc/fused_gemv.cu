@@ -809,7 +809,10 @@ static int launch_stream_nt(const void *W, const void *X, void *Y, int M, int N,
         const size_t ring_room = kStreamSmemLimit - stream_fixed_smem(N, Bg, red_in_ring);
         size_t best = 0;
         kc = 0;
-        for (int cand = 16; cand >= 1; cand >>= 1) {
+        // (kc = 4 first: with four warps per group it is the one-batch-per-warp cut, so it wins ties)
+        const int order[5] = {4, 16, 8, 2, 1};
+        for (int oi = 0; oi < 5; ++oi) {
+            const int cand = order[oi];
             if (only_kc && cand != only_kc) continue;
             if ((N / 64) % cand || (size_t)group_rows * 128 * cand > 32 * 1024) continue;
             const int sb = ((group_rows * 128 * cand) + 1023) & ~1023;
