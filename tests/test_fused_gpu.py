@@ -216,10 +216,12 @@ def test_output_of_more_than_2_31_elements(pkg, dtype, out_dtype, layout):
 
 @pytest.mark.parametrize("M,N,B", [(4096, 256, 2), (300, 1024, 8), (6000, 4096, 24), (1000, 8192, 8),
                                    (4741, 512, 12), (77, 4096, 40), (4096, 2048, 5), (10000, 256, 1),
-                                   (9000, 4096, 16), (8, 8192, 4), (29, 1024, 32)])
+                                   (9000, 4096, 16), (8, 8192, 4), (29, 1024, 32),
+                                   (7000, 2048, 4), (20000, 1024, 8), (6000, 1024, 32), (12000, 8192, 2)])
 def test_bf16_gemv_streaming_path_shapes(pkg, oracle, M, N, B):
     """The bf16 path for 256 <= N <= 8192: every copy-in variant of X (B = 1, 2, 4, multiples of 8, others),
-    1 to 4 column tiles, column splits (B > 32), one and several row groups per CTA, ragged last rows."""
+    1 to 4 column tiles, column splits (B > 32), one and several row groups per CTA (the latter with two warp
+    groups of eight on 8 x 64 k items where N allows, four of four otherwise), ragged last rows."""
     g = torch.Generator().manual_seed(1000 + M + N + B)
     W = (torch.randn(M, N, generator=g) / N ** 0.5).bfloat16()
     X = torch.randn(N, B, generator=g).bfloat16()
