@@ -83,6 +83,34 @@ def test_two_gpu_row_sharded_gemv(tmp_path):
 
 
 @pytest.mark.gpu
+def test_row_sharded_gemv_on_one_rank(tmp_path):
+    """The degenerate split: one rank holds all rows, there is no peer, and the call is the plain GEMV writing into
+    the wrapper's result buffer (runs on any box)."""
+    script = tmp_path / "worker.py"
+    script.write_text(textwrap.dedent(f"""
+        import importlib, sys
+        sys.path.insert(0, {str(ROOT)!r})
+        import torch, torch.distributed as dist
+        pkg = importlib.import_module("6s894_project_2025_b200")
+        torch.cuda.set_device(0)
+        dist.init_process_group("gloo")
+        g = torch.Generator().manual_seed(5)
+        W = (torch.randn(1000, 2048, generator=g) / 45).bfloat16().cuda()
+        op = pkg.RowShardedGemv(W, 1000, 8)
+        for B in (8, 3, 8):
+            X = torch.randn(2048, B, generator=g).bfloat16().cuda()
+            assert torch.equal(op(X), pkg.fused_ht_gemv(W, X))
+        op.close()
+        assert pkg.device_status() == 0
+        dist.destroy_process_group()
+        print("ok")
+    """))
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29647", RANK="0", WORLD_SIZE="1")
+    r = subprocess.run([sys.executable, str(script)], capture_output=True, text=True, env=env, timeout=300)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stdout + r.stderr
+
+
+@pytest.mark.gpu
 def test_two_gpu_row_sharded_gemv_with_peer_stores(tmp_path):
     """The same split with the exchange inside the kernel: every GPU sends its rows of Y, tagged with the number of
     the call, into a slot array on the other GPU through peer-mapped pointers and collects the other's rows from its
