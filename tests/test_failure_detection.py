@@ -32,7 +32,8 @@ def test_bounded_wait_gives_up_and_context_survives(pkg, lib):
 def test_row_sharded_gemv_gives_up_on_a_peer_that_never_sends(pkg, lib):
     """The one cross-GPU wait of the library, run out on one GPU: a row-sharded GEMV call whose "peer" is a slot array
     that nothing fills.  The kernel computes its own rows, waits a second for the other half, gives up with
-    B200HT_ERR_TIMEOUT in the status word, and the context keeps working."""
+    B200HT_ERR_TIMEOUT in the status word, and the context keeps working.  The second rank of the same exchange, run
+    afterwards on the same GPU, finds the first rank's values waiting and completes the result."""
     import ctypes
     l = lib.load()
     assert l.b200ht_device_status(1) == 0
@@ -63,6 +64,20 @@ def test_row_sharded_gemv_gives_up_on_a_peer_that_never_sends(pkg, lib):
     assert bool((peer_slots[half * B:] == 0).all())
     assert int(count[0]) == 0 and int(count[1]) == 1          # scratch word back at zero, one call counted
     assert pkg.device_status() == 0
+    # Now the other rank of that exchange, on the same GPU: its slot array is the one the first call filled, so it
+    # finds the first half there at once, adds its own rows, and holds the complete result.
+    y_full1 = torch.full((M, B), 7.0, device="cuda")
+    count1 = torch.zeros(2, dtype=torch.int32, device="cuda")
+    peers1 = (ctypes.c_void_p * 1)(my_slots.data_ptr())
+    rc = l.b200ht_fused_gemv_peers(W[half:].data_ptr(), X.data_ptr(), y_full1.data_ptr(), M - half, N, B, lib.BF16,
+                                   lib.F32, float(N ** -0.5), half, M, 1, peers1, peer_slots.data_ptr(),
+                                   count1.data_ptr(), 1, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, lib.error_string(rc)
+    torch.cuda.synchronize()
+    assert l.b200ht_device_status(1) == 0
+    full = pkg.fused_ht_gemv(W, X)
+    assert float((y_full1 - full).norm() / full.norm()) < 1e-5
+    assert torch.equal(y_full1[:half], ref)                   # the collected rows are the sender's values, bit for bit
 
 
 def test_missing_rank_is_detected_by_the_survivor(tmp_path):
